@@ -1,8 +1,9 @@
-from .specs import BlockSpec, ConfigError, LayerCall, ModelPlan, PartSpec
+from .specs import BlockSpec, ConfigError, JunctionCall, LayerCall, ModelPlan, PartSpec, WeightBinding
 from .registry import (config_class_for, config_from_dict, known_architectures, load_config,
                        register_architecture)
-from .llama4 import Llama4Config, RopeScaling, WeightBinding
+from .llama4 import Llama4Config, RopeScaling
+from .sezazen import SezazenConfig
 
-__all__ = ["BlockSpec", "ConfigError", "LayerCall", "ModelPlan", "PartSpec", "config_class_for",
+__all__ = ["BlockSpec", "ConfigError", "JunctionCall", "LayerCall", "ModelPlan", "PartSpec", "config_class_for",
            "config_from_dict", "known_architectures", "load_config", "register_architecture",
-           "Llama4Config", "RopeScaling", "WeightBinding"]
+           "Llama4Config", "RopeScaling", "SezazenConfig", "WeightBinding"]

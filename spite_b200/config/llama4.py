@@ -12,17 +12,7 @@ from dataclasses import dataclass, field, asdict
 from typing import Optional
 
 from .registry import register_architecture
-from .specs import BlockSpec, ConfigError, LayerCall, ModelPlan, PartSpec
-
-
-@dataclass(frozen=True)
-class WeightBinding:
-    """A parameter of the plan and the checkpoint tensor that fills it."""
-    target: str                 # e.g. "layers.3.ffn.experts_down"
-    source: str                 # checkpoint tensor name
-    source_shape: tuple         # exact shape expected in the file
-    transform: Optional[str] = None   # a registered weight transform (spite_b200.weights.register_weight_transform)
-    init: str = "normal"        # how the random-weights mode fills it: "normal" | "ones"
+from .specs import BlockSpec, ConfigError, LayerCall, ModelPlan, PartSpec, WeightBinding
 
 
 @dataclass(frozen=True)

@@ -41,7 +41,7 @@ def config_class_for(name: str):
 
 
 def config_from_dict(d: dict):
-    archs = d.get("architectures")
+    archs = d.get("architectures", d.get("architecture"))      # some formats name one architecture, as a string
     if isinstance(archs, str):
         archs = [archs]
     if not archs or not isinstance(archs, (list, tuple)):

@@ -11,7 +11,7 @@ from __future__ import annotations
 import torch
 
 from ..cache import FixedState, PagedKV
-from ..config import ConfigError, ModelPlan, load_config
+from ..config import ConfigError, JunctionCall, ModelPlan, load_config
 from ..kernels import build as kernel_build
 from ..parts import BuildContext, ParamSpec, build_part
 from ..parts.base import _REGISTRIES
@@ -46,9 +46,14 @@ class Model:
             if spec.arrangement not in blocks:
                 raise ConfigError(f"no block arrangement {spec.arrangement!r}; known: {', '.join(sorted(blocks))}")
             self.blocks.append(blocks[spec.arrangement](self.ctx, spec))
+        self.junctions = [build_part("junction", spec, self.ctx) for spec in plan.junctions]
         self.final_norm = build_part("norm", plan.final_norm, self.ctx)
         self.embed_table = None
         self.head_weight = None
+        self.position_table = None
+        #: if set, called as `layer_tap(i, h)` after the i-th layer run of the order with the float32 residual
+        #: stream (for comparing a model layer by layer; the step then cannot be captured in a graph)
+        self.layer_tap = None
         self._check_caches()
 
     # ------------------------------------------------------------------ structure
@@ -57,11 +62,15 @@ class Model:
         for i, b in enumerate(self.blocks):
             for cname, child in b.children().items():
                 yield f"layers.{i}.{cname}", child
+        for i, j in enumerate(self.junctions):
+            yield f"junctions.{i}", j
         yield "final_norm", self.final_norm
 
     def param_specs(self) -> dict[str, ParamSpec]:
         p = self.plan
         out = {"embed.weight": ParamSpec((p.vocab_size, p.hidden_size))}
+        if p.position_table is not None:
+            out["positions.weight"] = ParamSpec((p.position_table, p.hidden_size))
         for name, part in self.parts():
             for pname, spec in part.param_specs().items():
                 out[f"{name}.{pname}"] = spec
@@ -81,12 +90,13 @@ class Model:
         """True if a step's kernels can be captured in a CUDA graph: the product kernel set
         and parts that launch nothing but its kernels and never read device data on the host."""
         from ..kernels.cuda import CudaKernels
-        return isinstance(self.kernels, CudaKernels) and all(part.graph_safe for _, part in self.parts()) \
+        return isinstance(self.kernels, CudaKernels) and self.layer_tap is None \
+            and all(part.graph_safe for _, part in self.parts()) \
             and all(getattr(b, "graph_safe", False) for b in self.blocks)
 
     def _check_caches(self):
         self._cache_specs = {}
-        for call in self.plan.order:
+        for call in self.plan.layer_calls():
             req = self.blocks[call.layer].cache_request()
             have = self._cache_specs.get(call.cache)
             if have is None:
@@ -112,6 +122,8 @@ class Model:
         self.embed_table = tensors["embed.weight"].to(self.device, self.dtype).contiguous()
         self.head_weight = self.embed_table if self.plan.tie_word_embeddings else \
             tensors["head.weight"].to(self.device, self.dtype).contiguous()
+        if self.plan.position_table is not None:
+            self.position_table = tensors["positions.weight"].to(self.device, self.dtype).contiguous()
         for name, part in self.parts():
             own = {p: tensors[f"{name}.{p}"].to(self.device) for p in part.param_specs()}
             part.bind(own)
@@ -132,6 +144,8 @@ class Model:
         self.embed_table = make("embed.weight", ParamSpec((p.vocab_size, p.hidden_size)))
         self.head_weight = self.embed_table if p.tie_word_embeddings else \
             make("head.weight", ParamSpec((p.vocab_size, p.hidden_size)))
+        if p.position_table is not None:
+            self.position_table = make("positions.weight", ParamSpec((p.position_table, p.hidden_size)))
         for name, part in self.parts():
             part.bind({pn: make(f"{name}.{pn}", ps) for pn, ps in part.param_specs().items()})
         return self
@@ -140,6 +154,8 @@ class Model:
         n = self.embed_table.numel() * self.embed_table.element_size()
         if self.head_weight is not self.embed_table:
             n += self.head_weight.numel() * self.head_weight.element_size()
+        if self.position_table is not None:
+            n += self.position_table.numel() * self.position_table.element_size()
         return n + sum(part.weight_bytes() for _, part in self.parts())
 
     # ------------------------------------------------------------------ construction
@@ -175,9 +191,24 @@ class Model:
         k = self.kernels
         p = self.plan
         h = torch.empty((batch.n_tokens, p.hidden_size), dtype=torch.float32, device=self.device)
-        k.embed(self.embed_table, batch.token_ids, h, scale=p.embedding_scale)
+        if self.position_table is None:
+            k.embed(self.embed_table, batch.token_ids, h, scale=p.embedding_scale)
+        else:
+            k.embed(self.embed_table, batch.token_ids, h, scale=p.embedding_scale,
+                    position_table=self.position_table, positions=batch.positions)
+        h0 = None
+        if self.junctions:                       # the embedding's output, which the junctions mix back in
+            h0 = torch.empty_like(h)
+            h0.copy_(h)
+        runs = 0
         for call in p.order:
+            if isinstance(call, JunctionCall):
+                self.junctions[call.junction].forward(h, h0, batch, call.step)
+                continue
             self.blocks[call.layer].forward(h, batch, storage.layer_cache(call.cache, call.write_cache))
+            if self.layer_tap is not None:
+                self.layer_tap(runs, h)
+            runs += 1
         R = batch.logit_rows.numel()
         logits = torch.empty((R, p.vocab_size), dtype=torch.float32, device=self.device)
         if R:

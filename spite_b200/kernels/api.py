@@ -49,8 +49,14 @@ class KernelSet:
         return {}
 
     # ---- elementwise
-    def embed(self, table, token_ids, out_h, *, scale=1.0):
-        """out_h[m, :] (float32) = table[token_ids[m], :] (T) * scale."""
+    def embed(self, table, token_ids, out_h, *, scale=1.0, position_table=None, positions=None):
+        """out_h[m, :] (float32) = table[token_ids[m], :] (T) * scale; with a `position_table` [P, d] (T)
+        and `positions` [M] int32, + position_table[positions[m], :] (not scaled)."""
+        raise NotImplementedError
+
+    def pack_pair(self, a, b, out, *, refill=None):
+        """out[m, :] (T) = [a[m, :]; b[m, :]] for two float32 streams [M, d]; with `refill` [d] float32 every
+        row of `a` becomes that vector afterwards (the stream is restarted for a product that adds into it)."""
         raise NotImplementedError
 
     def transform_logits(self, logits, *, scale=1.0, softcap=None):
@@ -63,10 +69,11 @@ class KernelSet:
         raise NotImplementedError
 
     # ---- matrix products: y = x W^T with W [out, in]
-    def linear(self, x, w, out, *, accumulate=False, row_scale=None):
+    def linear(self, x, w, out, *, accumulate=False, row_scale=None, activation=None):
         """out[M, N] = x[M, K] @ w[N, K]^T.  `out` is T, or float32 (logits); with
         `accumulate` it is float32 and the product is added to it (residual stream).
-        `row_scale` [M] float32 multiplies the product's rows."""
+        `row_scale` [M] float32 multiplies the product's rows.  `activation` "relu2" (with an
+        output of type T): out = relu(s y)^2."""
         raise NotImplementedError
 
     def linear_swiglu(self, x, w_gate_up, out, *, row_scale=None):
@@ -76,6 +83,11 @@ class KernelSet:
     def grouped_linear_swiglu(self, x, w_gate_up, sorted_rows, offsets, row_scale, out):
         """Row i of `out` [M, F] (sorted order) is the SwiGLU of token sorted_rows[i] through the
         expert whose range of `offsets` holds i; w_gate_up [E, 2F, K]; row_scale [M] by token."""
+        raise NotImplementedError
+
+    def grouped_linear_act(self, x, w_up, sorted_rows, offsets, row_scale, out, *, activation="relu2"):
+        """Row i of `out` [M, F] (sorted order) is act(s * (x[sorted_rows[i]] @ w_up[e]^T)) for the expert e whose
+        range of `offsets` holds i; w_up [E, F, K]; row_scale [M] by token; "relu2": act(y) = relu(y)^2."""
         raise NotImplementedError
 
     def grouped_linear_accumulate(self, a, w_down, sorted_rows, offsets, h):
@@ -98,8 +110,10 @@ class KernelSet:
         (floor, scale) or None: q *= ln(floor((pos + 1) / floor) + 1) * scale + 1."""
         raise NotImplementedError
 
-    def paged_attention(self, q, out, batch, cache, *, num_heads, window, softmax_scale, cache_settled=False):
+    def paged_attention(self, q, out, batch, cache, *, num_heads, window, softmax_scale, cache_settled=False,
+                        sink_logit=None):
         """out[M, nq hd] = softmax(q K^T * scale over the visible cached keys) V.
+        `sink_logit`: the softmax's denominator also holds exp(sink_logit), a key without a value.
         `cache_settled`: the caller promises that the cache rows of positions before each request's first
         token of this step were written by earlier steps (not by the one or two kernels launched just
         before this call), so a kernel may fetch them while the kernel before still runs."""

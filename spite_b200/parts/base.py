@@ -14,6 +14,9 @@ Kinds of parts and what each must provide:
   feed_forward   `forward(x, h, batch)`: adds its output into h
   block          `places` (name -> family of each part it is made of),
                  `forward(h, batch, cache)`: one layer on the residual stream h
+  junction       `forward(h, h0, batch, step)`: rewrites h between two layers; h0 is the
+                 embedding's output, `step` how often the junction has run before in this pass
+                 through the model
 
 `h` is the float32 residual stream [M, hidden]; `x` is a normalised copy in the
 activation type.
@@ -28,7 +31,7 @@ import torch
 from ..config.specs import ConfigError, PartSpec
 
 _REGISTRIES: dict[str, dict[str, type]] = {
-    "norm": {}, "position": {}, "mixer": {}, "feed_forward": {}, "block": {},
+    "norm": {}, "position": {}, "mixer": {}, "feed_forward": {}, "block": {}, "junction": {},
 }
 
 
@@ -58,6 +61,10 @@ def register_feed_forward(kind):
 
 def register_block(kind):
     return _register("block", kind)
+
+
+def register_junction(kind):
+    return _register("junction", kind)
 
 
 def registered(family: str) -> list[str]:
@@ -158,6 +165,12 @@ class Mixer(Part):
 
 class FeedForward(Part):
     def forward(self, x, h, batch):
+        raise NotImplementedError
+
+
+class Junction(Part):
+    """Something that happens to the residual stream between two layers of the run order."""
+    def forward(self, h, h0, batch, step: int):
         raise NotImplementedError
 
 

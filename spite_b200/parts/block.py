@@ -1,7 +1,7 @@
 """How the parts of one layer are arranged.
 
 `prenorm_residual` (crates/spite-models/src/llama/llama4.rs:126-127,202-211,272-274):
-    h += mixer(norm_a(h));  h += feed_forward(norm_b(h))
+    h += mixer(norm_a(h));  h += feed_forward(norm_b(h))      (the second half may be left out)
 The residual stream h stays float32; the sums are done by the epilogues of the
 mixer's and the feed-forward's last products.
 """
@@ -16,10 +16,12 @@ from .base import Block, register_block
 class PreNormResidual(Block):
     graph_safe = True
     places = {"mixer_norm": "norm", "mixer": "mixer", "ffn_norm": "norm", "ffn": "feed_forward"}
+    optional = ("ffn_norm", "ffn")           # a layer may be a mixer alone
 
     def forward(self, h, batch, cache):
         x = torch.empty(h.shape, dtype=self.ctx.dtype, device=h.device)
         self.mixer_norm.forward(h, x)
         self.mixer.forward(x, h, batch, cache)
-        self.ffn_norm.forward(h, x)
-        self.ffn.forward(x, h, batch)
+        if self.ffn is not None:
+            self.ffn_norm.forward(h, x)
+            self.ffn.forward(x, h, batch)

@@ -52,19 +52,29 @@ class MoESigmoidPrescaled(FeedForward):
     unweighted (moe.rs:188-191); a shared expert runs on the unscaled token
     (llama4.rs:231-256).
 
+    `activation` says what an expert is: "swiglu", down(silu(gate x) * (up x)), or
+    "relu2", down(relu(up x)^2) without a gate.  The shared expert has the same form
+    and a size of its own (`shared_size`; 0: none).
+
     Because the expert's two input products are linear in the token, the factor
     is applied to their float32 sums in the epilogue: silu(s g) * (s u) with
-    g, u the products of the unscaled token.  That equals the pre-scaled form
-    and spares rounding the scaled token to the activation type.
+    g, u the products of the unscaled token (relu(s u)^2 without a gate).  That equals
+    the pre-scaled form and spares rounding the scaled token to the activation type.
     """
     graph_safe = True
     kernel_libraries = ("gemm_simt", "moe")
 
+    ACTIVATIONS = ("swiglu", "relu2")
+
     def __init__(self, ctx, hidden_size: int, num_experts: int, top_k: int, expert_size: int,
-                 shared_size: int = 0):
+                 shared_size: int = 0, activation: str = "swiglu"):
         super().__init__(ctx)
         if not 1 <= top_k <= num_experts:
             raise ConfigError(f"top_k {top_k} must lie in 1..{num_experts}")
+        if activation not in self.ACTIVATIONS:
+            raise ConfigError(f"unknown expert activation {activation!r}; known: {', '.join(self.ACTIVATIONS)}")
+        self.activation = activation
+        self.gated = activation == "swiglu"
         self.d, self.E, self.top_k = int(hidden_size), int(num_experts), int(top_k)
         self.f, self.fs = int(expert_size), int(shared_size)
         self.router = self.w_gate_up = self.w_down = self.ws_gate_up = self.ws_down = None
@@ -73,21 +83,27 @@ class MoESigmoidPrescaled(FeedForward):
 
     def param_specs(self):
         d, E, f, fs = self.d, self.E, self.f, self.fs
-        specs = {"router": ParamSpec((E, d)), "experts_gate_up": ParamSpec((E, 2 * f, d)),
-                 "experts_down": ParamSpec((E, d, f))}
+        specs = {"router": ParamSpec((E, d)), "experts_down": ParamSpec((E, d, f))}
+        if self.gated:
+            specs["experts_gate_up"] = ParamSpec((E, 2 * f, d))
+        else:
+            specs["experts_up"] = ParamSpec((E, f, d))
         if fs:
-            specs.update({"shared_gate_proj": ParamSpec((fs, d)), "shared_up_proj": ParamSpec((fs, d)),
-                          "shared_down_proj": ParamSpec((d, fs))})
+            if self.gated:
+                specs["shared_gate_proj"] = ParamSpec((fs, d))
+            specs.update({"shared_up_proj": ParamSpec((fs, d)), "shared_down_proj": ParamSpec((d, fs))})
         return specs
 
     def bind(self, params):
         dt = self.ctx.dtype
         # router logits are float32 sums of float32 weights in both kernel sets
         self.router = params["router"].to(torch.float32).contiguous()
-        self.w_gate_up = params["experts_gate_up"].to(dt).contiguous()
+        # (without a gate `w_gate_up` holds the up rows alone)
+        self.w_gate_up = params["experts_gate_up" if self.gated else "experts_up"].to(dt).contiguous()
         self.w_down = params["experts_down"].to(dt).contiguous()
         if self.fs:
-            self.ws_gate_up = torch.cat([params["shared_gate_proj"].to(dt), params["shared_up_proj"].to(dt)], 0).contiguous()
+            first = [params["shared_gate_proj"].to(dt)] if self.gated else []
+            self.ws_gate_up = torch.cat(first + [params["shared_up_proj"].to(dt)], 0).contiguous()
             self.ws_down = params["shared_down_proj"].to(dt).contiguous()
 
     def weight_bytes(self):
@@ -126,7 +142,10 @@ class MoESigmoidPrescaled(FeedForward):
         self.last_routing = routing
         if self.fs:
             a = torch.empty((M, self.fs), dtype=x.dtype, device=x.device)
-            k.linear_swiglu(x, self.ws_gate_up, a)
+            if self.gated:
+                k.linear_swiglu(x, self.ws_gate_up, a)
+            else:
+                k.linear(x, self.ws_gate_up, a, activation=self.activation)
             k.linear(a, self.ws_down, h, accumulate=True)
         if side is not None:
             main.wait_event(routed)
@@ -135,8 +154,12 @@ class MoESigmoidPrescaled(FeedForward):
                     t.record_stream(main)                        # made on the side stream, read on this one
         for slot in range(self.top_k):
             a = torch.empty((M, self.f), dtype=x.dtype, device=x.device)
-            k.grouped_linear_swiglu(x, self.w_gate_up, routing.sorted_rows[slot], routing.offsets[slot],
-                                    routing.weights[slot], a)
+            if self.gated:
+                k.grouped_linear_swiglu(x, self.w_gate_up, routing.sorted_rows[slot], routing.offsets[slot],
+                                        routing.weights[slot], a)
+            else:
+                k.grouped_linear_act(x, self.w_gate_up, routing.sorted_rows[slot], routing.offsets[slot],
+                                     routing.weights[slot], a, activation=self.activation)
             k.grouped_linear_accumulate(a, self.w_down, routing.sorted_rows[slot], routing.offsets[slot], h)
 
     def _side_stream(self, x):

@@ -64,9 +64,18 @@ def _transpose_last2(t):
     return t.transpose(-1, -2).contiguous()
 
 
+def _sources(binding) -> tuple:
+    src = binding.source
+    return (src,) if isinstance(src, str) else tuple(src)
+
+
 def apply_binding(binding, tensor, device="cpu"):
-    """The parameter that `binding` makes of the checkpoint tensor `tensor`."""
-    t = tensor.to(storage_dtype(tensor.dtype)).to(device)
+    """The parameter that `binding` makes of the checkpoint tensor `tensor` (a list of tensors for a binding
+    that stacks several)."""
+    if isinstance(tensor, (list, tuple)):
+        t = torch.stack([x.to(storage_dtype(x.dtype)).to(device) for x in tensor], 0)
+    else:
+        t = tensor.to(storage_dtype(tensor.dtype)).to(device)
     if binding.transform is None:
         return t
     try:
@@ -81,14 +90,17 @@ def bind_tensors(config, source: dict, device="cpu", folder="(tensors in memory)
     """The same binding for checkpoint tensors that are already in memory: `source` maps checkpoint
     tensor names (without prefix) to tensors.  One `WeightError` lists what does not fit."""
     bindings = config.weight_bindings()
-    missing = [(b.source, b.source_shape) for b in bindings if b.source not in source]
-    wrong = [(b.source, tuple(source[b.source].shape), b.source_shape) for b in bindings
-             if b.source in source and tuple(source[b.source].shape) != tuple(b.source_shape)]
-    used = {b.source for b in bindings}
-    unexpected = sorted(n for n in source if n not in used)
+    named = [(b, n) for b in bindings for n in _sources(b)]
+    missing = [(n, b.source_shape) for b, n in named if n not in source]
+    wrong = [(n, tuple(source[n].shape), b.source_shape) for b, n in named
+             if n in source and tuple(source[n].shape) != tuple(b.source_shape)]
+    used = {n for _, n in named}
+    ignored = tuple(getattr(config, "ignored_prefixes", ()))
+    unexpected = sorted(n for n in source if n not in used and not (ignored and n.startswith(ignored)))
     if missing or wrong or unexpected:
         raise WeightError(folder, missing, wrong, unexpected)
-    return {b.target: apply_binding(b, source[b.source], device) for b in bindings}
+    return {b.target: apply_binding(b, source[b.source] if isinstance(b.source, str) else
+                                    [source[n] for n in _sources(b)], device) for b in bindings}
 
 
 def storage_dtype(file_dtype: torch.dtype) -> torch.dtype:
@@ -114,24 +126,25 @@ def load_bound_tensors(folder, config, device="cpu") -> dict[str, torch.Tensor]:
         prefixes = getattr(config, "checkpoint_prefixes", ("",))
         ignored = tuple(getattr(config, "ignored_prefixes", ()))
         # the prefix under which most expected tensors are found
-        prefix = max(prefixes, key=lambda p: sum((p + b.source) in where for b in bindings))
+        prefix = max(prefixes, key=lambda p: sum((p + n) in where for b in bindings for n in _sources(b)))
         missing, wrong, used = [], [], set()
         for b in bindings:
-            name = prefix + b.source
-            if name not in where:
-                missing.append((name, b.source_shape))
-                continue
-            used.add(name)
-            got = where[name].entries[name][1]
-            if tuple(got) != tuple(b.source_shape):
-                wrong.append((name, got, b.source_shape))
-        unexpected = sorted(n for n in where if n not in used and not n.startswith(ignored))
+            for src in _sources(b):
+                name = prefix + src
+                if name not in where:
+                    missing.append((name, b.source_shape))
+                    continue
+                used.add(name)
+                got = where[name].entries[name][1]
+                if tuple(got) != tuple(b.source_shape):
+                    wrong.append((name, got, b.source_shape))
+        unexpected = sorted(n for n in where if n not in used and not (ignored and n.startswith(ignored)))
         if missing or wrong or unexpected:
             raise WeightError(folder, missing, wrong, unexpected)
         out = {}
         for b in bindings:
-            name = prefix + b.source
-            out[b.target] = apply_binding(b, where[name].tensor(name), device)
+            got = [where[prefix + n].tensor(prefix + n) for n in _sources(b)]
+            out[b.target] = apply_binding(b, got[0] if isinstance(b.source, str) else got, device)
         return out
     finally:
         for f in files:

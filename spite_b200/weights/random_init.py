@@ -36,8 +36,8 @@ def random_checkpoint_tensors(config, seed: int = 0, std: float = 0.02, dtype=to
     """{checkpoint tensor name: tensor} for `config`, as `write_random_model` would store them (the same
     values on the CPU; another device has its own generator).  For models that are too large to be worth
     writing: `Model.from_tensors` binds them like a checkpoint read from disk."""
-    return {b.source: random_tensor(seed, b.source, b.source_shape, b.init, std, dtype, device)
-            for b in config.weight_bindings()}
+    return {name: random_tensor(seed, name, b.source_shape, b.init, std, dtype, device)
+            for b in config.weight_bindings() for name in b.sources}
 
 
 def write_random_model(folder, config, seed: int = 0, std: float = 0.02, dtype=torch.bfloat16):

@@ -24,8 +24,16 @@ class TorchReferenceKernels(KernelSet):
         self.acc = acc
 
     # ---- elementwise
-    def embed(self, table, token_ids, out_h, *, scale=1.0):
-        out_h.copy_(table[token_ids.long()].float() * scale)
+    def embed(self, table, token_ids, out_h, *, scale=1.0, position_table=None, positions=None):
+        x = table[token_ids.long()].to(self.acc) * scale
+        if position_table is not None:
+            x = x + position_table[positions.long()].to(self.acc)
+        out_h.copy_(x.to(out_h.dtype))
+
+    def pack_pair(self, a, b, out, *, refill=None):
+        out.copy_(torch.cat([a, b], -1).to(out.dtype))
+        if refill is not None:
+            a.copy_(refill.to(a.dtype)[None, :].expand_as(a))
 
     def clear_pages(self, kv, page_ids):
         if page_ids:
@@ -46,10 +54,13 @@ class TorchReferenceKernels(KernelSet):
     def _mm(self, x, w):
         return x.to(self.acc) @ w.to(self.acc).T
 
-    def linear(self, x, w, out, *, accumulate=False, row_scale=None):
+    def linear(self, x, w, out, *, accumulate=False, row_scale=None, activation=None):
         y = self._mm(x, w)
         if row_scale is not None:
             y = y * row_scale.to(self.acc)[:, None]
+        if activation is not None:
+            assert activation == "relu2" and not accumulate
+            y = torch.relu(y) ** 2
         if accumulate:
             out.add_(y.to(out.dtype))
         else:
@@ -80,6 +91,20 @@ class TorchReferenceKernels(KernelSet):
             if row_scale is not None:
                 y = y * row_scale[tok].to(self.acc)[:, None]
             out[lo:hi] = (self._silu(y[:, :F]) * y[:, F:]).to(out.dtype)
+
+    def grouped_linear_act(self, x, w_up, sorted_rows, offsets, row_scale, out, *, activation="relu2"):
+        assert activation == "relu2"
+        off = offsets.tolist()
+        rows = sorted_rows.long()
+        for e in range(w_up.shape[0]):
+            lo, hi = off[e], off[e + 1]
+            if hi == lo:
+                continue
+            tok = rows[lo:hi]
+            y = self._mm(x[tok], w_up[e])
+            if row_scale is not None:
+                y = y * row_scale[tok].to(self.acc)[:, None]
+            out[lo:hi] = (torch.relu(y) ** 2).to(out.dtype)
 
     def grouped_linear_accumulate(self, a, w_down, sorted_rows, offsets, h):
         E = w_down.shape[0]
@@ -142,7 +167,8 @@ class TorchReferenceKernels(KernelSet):
                 kv[0, page, :, p % P, :] = k[t].to(kv.dtype)
                 kv[1, page, :, p % P, :] = v[t].to(kv.dtype)
 
-    def paged_attention(self, q, out, batch, cache, *, num_heads, window, softmax_scale, cache_settled=False):
+    def paged_attention(self, q, out, batch, cache, *, num_heads, window, softmax_scale, cache_settled=False,
+                        sink_logit=None):
         kv = cache.kv
         nkv, P, hd = kv.shape[2], kv.shape[3], kv.shape[4]
         nq = num_heads
@@ -162,7 +188,10 @@ class TorchReferenceKernels(KernelSet):
             V = kv[1, pages, :, js % P, :].to(self.acc)
             for h in range(nq):
                 s = (K[:, h // group, :] @ qf[t, h]) * softmax_scale
-                w = torch.softmax(s, dim=0)
+                if sink_logit is None:
+                    w = torch.softmax(s, dim=0)
+                else:                                            # a key of that score and no value
+                    w = torch.softmax(torch.cat([s, s.new_tensor([sink_logit])]), dim=0)[:-1]
                 out[t, h * hd:(h + 1) * hd] = (w @ V[:, h // group, :]).to(out.dtype)
 
     # ---- mixture of experts
