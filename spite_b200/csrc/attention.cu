@@ -209,6 +209,13 @@ __global__ void __launch_bounds__(128) paged_attention_kernel(const AttentionPar
         }
         m = m_new;
     }
+    if (p.has_sink) {                                        // one more key, of score sink_logit and value zero
+        const float m_new = fmaxf(m, p.sink_logit);
+        const float corr = expf(m - m_new);
+        l = l * corr + expf(p.sink_logit - m_new);
+#pragma unroll
+        for (int r = 0; r < MAXD; ++r) acc[r] *= corr;
+    }
     const float inv = 1.0f / fmaxf(l, 1e-30f);
     T* out = (T*)p.out + ((size_t)t * nq + h) * hd;
 #pragma unroll

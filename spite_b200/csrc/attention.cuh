@@ -54,7 +54,20 @@ struct AttentionParams {
     int window_kind;
     int window_size;
     float softmax_scale;
+    int has_sink;               // the softmax's denominator also holds exp(sink_logit): a key every query sees
+    float sink_logit;           // and that has no value (with 0: one is added to the denominator)
 };
+
+// The sink folded into a finished softmax state: `m` and `l` are the maximum and the sum of exp(s - m) over the
+// real keys (natural-log units).  Afterwards l is the whole denominator relative to max(m, sink); the return
+// value is the factor by which the accumulated values shrink to the same reference.
+__device__ __forceinline__ float fold_sink(const AttentionParams& p, float m, float& l) {
+    if (!p.has_sink) return 1.f;
+    const float m2 = fmaxf(m, p.sink_logit);
+    const float f = (m == -INFINITY) ? 0.f : expf(m - m2);
+    l = l * f + expf(p.sink_logit - m2);
+    return f;
+}
 
 // What the tensor-core attention kernels need beyond the above.  Two kernels share a step:
 // segments of few tokens (decode) go to the one that splits the keys among blocks, segments

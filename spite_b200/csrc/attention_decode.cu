@@ -316,6 +316,7 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const __grid_const
         }
         if (x.n_splits == 1) {
             const int tok = t0 + r / G, head = kvh * G + r % G;
+            acc *= fold_sink(p, m, l);
             ((__nv_bfloat16*)p.out)[((size_t)tok * nq + head) * HD + d] = __float2bfloat16_rn(acc / fmaxf(l, 1e-30f));
         } else {
             __stcg(part + r * ROW + d, acc);
@@ -381,7 +382,8 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const __grid_const
             }
             l += warp_sum(ls);
         }
-        if (lane == 0) inv_s[r] = 1.0f / fmaxf(l, 1e-30f);
+        const float shrink = fold_sink(p, m, l);             // the sink joins once, after the splits have met
+        if (lane == 0) inv_s[r] = shrink / fmaxf(l, 1e-30f);
     }
     consumer_sync();
     for (int e = threadIdx.x; e < n_items; e += CONSUMERS * 32) {

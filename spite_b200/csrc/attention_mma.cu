@@ -265,6 +265,7 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const AttentionPar
         }
         const int tok = t0 + r / G, head = kvh * G + r % G;
         if (x.n_splits == 1) {
+            acc *= fold_sink(p, m, l);
             ((__nv_bfloat16*)p.out)[((size_t)tok * nq + head) * HD + d] = __float2bfloat16_rn(acc / fmaxf(l, 1e-30f));
         } else {
             // partial results are indexed by the block's place among this kernel's blocks, not by the
@@ -284,7 +285,8 @@ constexpr int MERGE_THREADS = 128;
 __global__ void __launch_bounds__(MERGE_THREADS) attn_merge_kernel(const float* __restrict__ o_part,
                                                                    const float* __restrict__ ml_part,
                                                                    __nv_bfloat16* __restrict__ out, int n_splits, int hd,
-                                                                   int num_heads, const AttnMmaExtra x) {
+                                                                   int num_heads, const AttnMmaExtra x,
+                                                                   const AttentionParams p) {
     __shared__ float w_s[MERGE_THREADS];
     __shared__ float scratch[33];
     pdl_wait();
@@ -317,8 +319,9 @@ __global__ void __launch_bounds__(MERGE_THREADS) attn_merge_kernel(const float* 
     m = fmaxf(fmaxf(scratch[0], scratch[1]), fmaxf(scratch[2], scratch[3]));
     const float w = ms > -INFINITY ? expf(ms - m) : 0.f;
     w_s[tid] = w;
-    const float l = block_sum(ls * w, scratch);             // syncs: w_s is visible afterwards
-    const float inv = 1.0f / fmaxf(l, 1e-30f);
+    float l = block_sum(ls * w, scratch);                   // syncs: w_s is visible afterwards
+    const float shrink = fold_sink(p, m, l);                // the sink joins once, after the splits have met
+    const float inv = shrink / fmaxf(l, 1e-30f);
     const float* o = o_part + row * n_splits * hd;
     __nv_bfloat16* dst = out + ((size_t)tok * num_heads + head) * hd;
     for (int d = tid; d < hd; d += MERGE_THREADS) {
@@ -379,6 +382,6 @@ SPITE_API int spite_paged_attention_mma(const AttentionParams* p, const StepToke
     if (rc != SPITE_OK || x->n_splits == 1) return rc;
     SPITE_LAUNCH(attn_merge_kernel, n_blocks * x->tokens_per_block * p->num_heads, MERGE_THREADS, 0, st,
                  (const float*)x->o_part, (const float*)x->ml_part, (__nv_bfloat16*)p->out, x->n_splits,
-                 c->head_dim, p->num_heads, *x);
+                 c->head_dim, p->num_heads, *x, *p);
     return spite_launch_status();
 }

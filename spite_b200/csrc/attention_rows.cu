@@ -236,7 +236,9 @@ __global__ void __launch_bounds__(WARPS * 32) attn_rows_kernel(const AttentionPa
         if (!row_ok[h]) continue;
         const int r = 16 * warp + g + 8 * h;
         const int tok = t0 + r / G, head = kvh * G + r % G;
-        const float inv = 1.0f / fmaxf(l_run[h], 1e-30f);
+        float l = l_run[h];
+        const float shrink = fold_sink(p, m_run[h], l);
+        const float inv = shrink / fmaxf(l, 1e-30f);
         __nv_bfloat16* dst = (__nv_bfloat16*)p.out + ((size_t)tok * nq + head) * HD + 2 * cc;
 #pragma unroll
         for (int n = 0; n < 2 * NK; ++n)

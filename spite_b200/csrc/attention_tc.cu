@@ -381,7 +381,13 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                     ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&gb.pv_done), (n_own - 1) & 1, abort_flag, err_word, 3, wait_limit));
                 if (ok && n_own > 0) {
                     fence_after();
-                    const float inv = 1.0f / fmaxf(l, 1e-30f);
+                    float shrink = 1.f;
+                    if (p.has_sink) {                              // the sink's score in this kernel's units (powers of two)
+                        const float sink2 = p.sink_logit * LOG2E, m2 = fmaxf(m_ref, sink2);
+                        shrink = (m_ref == -INFINITY) ? 0.f : exp2f(m_ref - m2);
+                        l = l * shrink + exp2f(sink2 - m2);
+                    }
+                    const float inv = shrink / fmaxf(l, 1e-30f);
                     __nv_bfloat16* dst = (__nv_bfloat16*)p.out + ((size_t)tok * nq + head) * HD;
 #pragma unroll 1
                     for (int c0 = 0; c0 < HD; c0 += 32) {

@@ -20,6 +20,44 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
     for (int i = threadIdx.x; i < d; i += blockDim.x) out[i] = to_f32(row[i]) * scale;
 }
 
+// h[m, :] = table[token[m], :] * scale + pos_table[positions[m], :]: learned position vectors, added unscaled;
+// the sum is float32
+template <typename T>
+__global__ void embed_positions_kernel(const T* __restrict__ table, const int* __restrict__ tokens,
+                                       const T* __restrict__ pos_table, const int* __restrict__ positions,
+                                       float* __restrict__ h, int d, int vocab, int n_positions, float scale) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int m = blockIdx.x;
+    const int tok = tokens[m], pos = positions[m];
+    float* out = h + (size_t)m * d;
+    if (tok < 0 || tok >= vocab || pos < 0 || pos >= n_positions) {   // the host rejects such steps before the launch
+        for (int i = threadIdx.x; i < d; i += blockDim.x) out[i] = 0.f;
+        return;
+    }
+    const T* row = table + (size_t)tok * d;
+    const T* pv = pos_table + (size_t)pos * d;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) out[i] = to_f32(row[i]) * scale + to_f32(pv[i]);
+}
+
+// out[m, :] = [a[m, :]; b[m, :]] in the activation type, for two float32 streams of width d; with `refill` every
+// row of a becomes that vector afterwards (a thread overwrites what it has just read itself)
+template <typename T>
+__global__ void pack_pair_kernel(float* __restrict__ a, const float* __restrict__ b, const float* __restrict__ refill,
+                                 T* __restrict__ out, int d) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t m = blockIdx.x;
+    float* ar = a + m * d;
+    const float* br = b + m * d;
+    T* o = out + m * 2 * d;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        o[i] = from_f32<T>(ar[i]);
+        o[d + i] = from_f32<T>(br[i]);
+        if (refill) ar[i] = refill[i];
+    }
+}
+
 // y[i, :] = x[r, :] * rsqrt(mean(x[r]^2) + eps) * gain      r = rows ? rows[i] : i
 // (crates/spite-models/src/dense.rs:175-181; the sum runs in float32)
 // One block per row.  The row stays in registers between the sum and the scaling: every thread
@@ -172,6 +210,38 @@ SPITE_API int spite_embed(int dtype, const void* table, const int* tokens, float
         SPITE_LAUNCH(embed_kernel<__nv_bfloat16>, n_tokens, threads, 0, st, (const __nv_bfloat16*)table, tokens, h, d, vocab, scale);
     else
         return SPITE_BAD_ARG;
+    return spite_launch_status();
+}
+
+SPITE_API int spite_embed_positions(int dtype, const void* table, const int* tokens, const void* pos_table,
+                                    const int* positions, float* h, int n_tokens, int d, int vocab, int n_positions,
+                                    float scale, void* stream) {
+    if (!table || !tokens || !pos_table || !positions || !h || n_tokens < 0 || d <= 0 || vocab <= 0 || n_positions <= 0 ||
+        !(scale == scale))
+        return SPITE_BAD_ARG;
+    if (dtype != SPITE_DT_F32 && dtype != SPITE_DT_BF16) return SPITE_BAD_ARG;
+    if (n_tokens == 0) return SPITE_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int threads = d >= 1024 ? 256 : 128;
+    if (dtype == SPITE_DT_F32)
+        SPITE_LAUNCH(embed_positions_kernel<float>, n_tokens, threads, 0, st, (const float*)table, tokens,
+                     (const float*)pos_table, positions, h, d, vocab, n_positions, scale);
+    else
+        SPITE_LAUNCH(embed_positions_kernel<__nv_bfloat16>, n_tokens, threads, 0, st, (const __nv_bfloat16*)table, tokens,
+                     (const __nv_bfloat16*)pos_table, positions, h, d, vocab, n_positions, scale);
+    return spite_launch_status();
+}
+
+// `a` and `b` float32 [n_rows, d] -> `out` [n_rows, 2 d] of `out_dtype`; `refill` [d] float32 or null
+SPITE_API int spite_pack_pair(int out_dtype, float* a, const float* b, const float* refill, void* out, int n_rows, int d,
+                              void* stream) {
+    if (!a || !b || !out || n_rows < 0 || d <= 0) return SPITE_BAD_ARG;
+    if (out_dtype != SPITE_DT_F32 && out_dtype != SPITE_DT_BF16) return SPITE_BAD_ARG;
+    if (n_rows == 0) return SPITE_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int threads = d >= 1024 ? 256 : 128;
+    if (out_dtype == SPITE_DT_F32) SPITE_LAUNCH(pack_pair_kernel<float>, n_rows, threads, 0, st, a, b, refill, (float*)out, d);
+    else SPITE_LAUNCH(pack_pair_kernel<__nv_bfloat16>, n_rows, threads, 0, st, a, b, refill, (__nv_bfloat16*)out, d);
     return spite_launch_status();
 }
 

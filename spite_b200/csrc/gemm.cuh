@@ -12,7 +12,7 @@
 #include "common.cuh"
 
 enum GemmEpilogue {
-    EPI_STORE = 0,        // C (activation type) = acc * scale
+    EPI_STORE = 0,        // C (activation type) = act(acc * scale), act by `activation`
     EPI_STORE_F32 = 1,    // C (float32) = acc * scale
     EPI_ADD_F32 = 2,      // C (float32) += acc * scale          (residual stream)
     EPI_SWIGLU = 3        // C (activation type) = silu(s*gate) * (s*up); W rows [0,N) gate, [N,2N) up
@@ -30,7 +30,21 @@ struct GemmParams {
     int n_groups, M, N, K;
     int epilogue;
     int scale_by_a_row;
+    int activation;       // SPITE_ACT_*: applied by EPI_STORE to the scaled sum before it is rounded
 };
+
+#define SPITE_ACT_NONE 0
+#define SPITE_ACT_RELU2 1        // relu(y)^2
+
+__device__ __forceinline__ float apply_activation(int act, float y) {
+    if (act == SPITE_ACT_RELU2) { y = fmaxf(y, 0.f); y *= y; }
+    return y;
+}
+
+// An activation goes with the plain store only.
+static inline bool activation_ok(const GemmParams* p) {
+    return p->activation == SPITE_ACT_NONE || (p->activation == SPITE_ACT_RELU2 && p->epilogue == EPI_STORE);
+}
 
 __device__ __forceinline__ float silu_f32(float g) { return g / (1.0f + expf(-g)); }
 

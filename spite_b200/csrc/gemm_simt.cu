@@ -101,7 +101,7 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const GemmParams p) {
             const int n = n0 + tx * TN + j;
             if (n >= p.N) continue;
             const size_t o = (size_t)crow * p.ldc + n;
-            if (EPI == EPI_STORE) ((T*)p.C)[o] = from_f32<T>(acc[0][i][j] * s);
+            if (EPI == EPI_STORE) ((T*)p.C)[o] = from_f32<T>(apply_activation(p.activation, acc[0][i][j] * s));
             else if (EPI == EPI_STORE_F32) ((float*)p.C)[o] = acc[0][i][j] * s;
             else if (EPI == EPI_ADD_F32) ((float*)p.C)[o] += acc[0][i][j] * s;
             else ((T*)p.C)[o] = from_f32<T>(silu_f32(acc[0][i][j] * s) * (acc[DUAL ? 1 : 0][i][j] * s));
@@ -130,7 +130,7 @@ int gemm_check(const GemmParams* p) {
     if (!p || !p->A || !p->W || !p->C) return SPITE_BAD_ARG;
     if (p->M < 0 || p->N <= 0 || p->K <= 0 || p->lda < p->K) return SPITE_BAD_ARG;
     if (p->group_offsets ? p->n_groups < 1 : p->n_groups != 1) return SPITE_BAD_ARG;
-    if (p->epilogue < 0 || p->epilogue > EPI_SWIGLU || p->ldc < p->N) return SPITE_BAD_ARG;
+    if (p->epilogue < 0 || p->epilogue > EPI_SWIGLU || p->ldc < p->N || !activation_ok(p)) return SPITE_BAD_ARG;
     return SPITE_OK;
 }
 

@@ -253,7 +253,7 @@ __global__ void __launch_bounds__(WARPS * 32, (NT <= 1 ? 2 : 1)) gemm_skinny_ker
             const int crow = p.c_rows ? p.c_rows[li] : li;
             const float sc = p.row_scale ? p.row_scale[p.scale_by_a_row ? arow : li] : 1.f;
             const size_t o = (size_t)crow * p.ldc + n;
-            if (EPI == EPI_STORE) ((__nv_bfloat16*)p.C)[o] = __float2bfloat16_rn(v * sc);
+            if (EPI == EPI_STORE) ((__nv_bfloat16*)p.C)[o] = __float2bfloat16_rn(apply_activation(p.activation, v * sc));
             else if (EPI == EPI_STORE_F32) ((float*)p.C)[o] = v * sc;
             else if (EPI == EPI_ADD_F32) ((float*)p.C)[o] += v * sc;
             else ((__nv_bfloat16*)p.C)[o] = __float2bfloat16_rn(silu_f32(v * sc) * (v2 * sc));
@@ -307,7 +307,7 @@ SPITE_API int spite_gemm_skinny(const GemmParams* p, int max_rows_per_group, int
     if (!p || !p->A || !p->W || !p->C) return SPITE_BAD_ARG;
     if (p->M < 0 || p->N <= 0 || p->K <= 0 || p->lda < p->K || p->ldc < p->N || n_blocks < 1) return SPITE_BAD_ARG;
     if (p->group_offsets ? p->n_groups < 1 : p->n_groups != 1) return SPITE_BAD_ARG;
-    if (p->epilogue < 0 || p->epilogue > EPI_SWIGLU) return SPITE_BAD_ARG;
+    if (p->epilogue < 0 || p->epilogue > EPI_SWIGLU || !activation_ok(p)) return SPITE_BAD_ARG;
     if (p->K % 32 || p->lda % 8) return SPITE_UNSUPPORTED;                 // 16-byte loads, 32-wide steps
     if (((uintptr_t)p->A | (uintptr_t)p->W) & 15) return SPITE_UNSUPPORTED;
     if (max_rows_per_group < 1 || p->n_groups > MAX_GROUPS || p->M > 64 * 8) return SPITE_UNSUPPORTED;

@@ -350,7 +350,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const GemmParams p
                 const int crow = p.c_rows ? p.c_rows[li] : li;
                 const float sc = p.row_scale ? p.row_scale[p.scale_by_a_row ? ar : li] : 1.f;
                 const size_t o = (size_t)crow * p.ldc + n;
-                if (EPI == EPI_STORE) ((__nv_bfloat16*)p.C)[o] = __float2bfloat16_rn(v * sc);
+                if (EPI == EPI_STORE) ((__nv_bfloat16*)p.C)[o] = __float2bfloat16_rn(apply_activation(p.activation, v * sc));
                 else if (EPI == EPI_STORE_F32) ((float*)p.C)[o] = v * sc;
                 else if (EPI == EPI_ADD_F32) ((float*)p.C)[o] += v * sc;
                 else ((__nv_bfloat16*)p.C)[o] = __float2bfloat16_rn(silu_f32(v * sc) * (v2 * sc));
@@ -560,7 +560,7 @@ SPITE_API int spite_gemm_stream(const GemmParams* p, int max_rows_per_group, int
     if (!p || !p->A || !p->W || !p->C) return SPITE_BAD_ARG;
     if (p->M < 0 || p->N <= 0 || p->K <= 0 || p->lda < p->K || p->ldc < p->N || n_blocks < 1 || n_splits < 1) return SPITE_BAD_ARG;
     if (p->group_offsets ? p->n_groups < 1 : p->n_groups != 1) return SPITE_BAD_ARG;
-    if (p->epilogue < 0 || p->epilogue > EPI_SWIGLU) return SPITE_BAD_ARG;
+    if (p->epilogue < 0 || p->epilogue > EPI_SWIGLU || !activation_ok(p)) return SPITE_BAD_ARG;
     if (k_slices != 1 && k_slices != 2 && k_slices != 4 && k_slices != 8) return SPITE_BAD_ARG;
     if (p->K % (BK * k_slices) || p->lda % 8 || (((uintptr_t)p->A | (uintptr_t)p->W) & 15)) return SPITE_UNSUPPORTED;
     if (k_slices == 8 && p->epilogue == EPI_SWIGLU) return SPITE_UNSUPPORTED;

@@ -292,7 +292,7 @@ SPITE_API int spite_gemm_tc(const GemmParams* p, int n_blocks, void* stream) {
     if (!p || !p->A || !p->W || !p->C) return SPITE_BAD_ARG;
     if (p->M < 0 || p->N <= 0 || p->K <= 0 || p->lda < p->K || p->ldc < p->N || n_blocks < 1) return SPITE_BAD_ARG;
     if (p->group_offsets ? p->n_groups < 1 : p->n_groups != 1) return SPITE_BAD_ARG;
-    if (p->epilogue < 0 || p->epilogue > EPI_SWIGLU) return SPITE_BAD_ARG;
+    if (p->epilogue < 0 || p->epilogue > EPI_SWIGLU || !activation_ok(p)) return SPITE_BAD_ARG;
     // TMA: 16-byte aligned bases and row pitches
     if (p->K % 8 || p->lda % 8 || (((uintptr_t)p->A | (uintptr_t)p->W) & 15)) return SPITE_UNSUPPORTED;
     if (p->n_groups > 1 && p->w_group_stride != (long long)(p->epilogue == EPI_SWIGLU ? 2 : 1) * p->N * p->K)

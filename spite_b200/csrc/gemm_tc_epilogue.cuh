@@ -37,7 +37,7 @@ __device__ __forceinline__ void drain_accumulator_row(const GemmParams& p, int l
             __nv_bfloat16* dst = (__nv_bfloat16*)p.C + o;
             float y[32];
 #pragma unroll
-            for (int i = 0; i < 32; ++i) y[i] = DUAL ? silu_f32(v[i] * sc) * (u[i] * sc) : v[i] * sc;
+            for (int i = 0; i < 32; ++i) y[i] = DUAL ? silu_f32(v[i] * sc) * (u[i] * sc) : apply_activation(p.activation, v[i] * sc);
             if (full && ((uintptr_t)dst & 15) == 0) {
 #pragma unroll
                 for (int i = 0; i < 32; i += 8) {

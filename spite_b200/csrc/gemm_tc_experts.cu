@@ -311,7 +311,7 @@ gemm_tc_experts_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
                         const float s = __shfl_sync(0xffffffffu, sc, t);
                         if (c0 + t < it.rows && n_ok) {
                             const float y = old[t] + v[t] * s;
-                            if (EPI == EPI_STORE) ((__nv_bfloat16*)p.C)[(size_t)r * p.ldc + n] = __float2bfloat16_rn(y);
+                            if (EPI == EPI_STORE) ((__nv_bfloat16*)p.C)[(size_t)r * p.ldc + n] = __float2bfloat16_rn(apply_activation(p.activation, y));
                             else ((float*)p.C)[(size_t)r * p.ldc + n] = y;
                         }
                     }
@@ -360,16 +360,16 @@ int launch(const GemmParams& p, int n_blocks, cudaStream_t st) {
 
 }  // namespace
 
-// A grouped product (`group_offsets` set) with the SwiGLU epilogue or the add into the float32 residual
-// stream (optionally scattered through `c_rows`).  `n_blocks`: number of multiprocessors (one persistent
+// A grouped product (`group_offsets` set) with the SwiGLU epilogue, the plain store (with an activation: an
+// expert without a gate) or the add into the float32 residual stream (optionally scattered through `c_rows`).  `n_blocks`: number of multiprocessors (one persistent
 // block each).  Groups of any size are taken (a large group is cut into token tiles and its weights
 // are then read once per tile: the caller sends such products to the kernels with 128-row tiles).
 SPITE_API int spite_gemm_tc_experts(const GemmParams* p, int n_blocks, void* stream) {
     if (!p || !p->A || !p->W || !p->C) return SPITE_BAD_ARG;
     if (p->M < 0 || p->N <= 0 || p->K <= 0 || p->lda < p->K || p->ldc < p->N || n_blocks < 1) return SPITE_BAD_ARG;
     if (!p->group_offsets || p->n_groups < 1) return SPITE_BAD_ARG;
-    if (p->epilogue < 0 || p->epilogue > EPI_SWIGLU) return SPITE_BAD_ARG;
-    if (p->epilogue != EPI_SWIGLU && p->epilogue != EPI_ADD_F32) return SPITE_UNSUPPORTED;
+    if (p->epilogue < 0 || p->epilogue > EPI_SWIGLU || !activation_ok(p)) return SPITE_BAD_ARG;
+    if (p->epilogue == EPI_STORE_F32) return SPITE_UNSUPPORTED;
     // TMA: 16-byte aligned bases and row pitches
     if (p->K % 8 || p->lda % 8 || (((uintptr_t)p->A | (uintptr_t)p->W) & 15)) return SPITE_UNSUPPORTED;
     if (p->w_group_stride != (long long)(p->epilogue == EPI_SWIGLU ? 2 : 1) * p->N * p->K)
@@ -377,5 +377,6 @@ SPITE_API int spite_gemm_tc_experts(const GemmParams* p, int n_blocks, void* str
     if (p->n_groups > MAX_LISTED) return SPITE_UNSUPPORTED;    // the groups with tokens are listed in shared memory
     if (p->M == 0) return SPITE_OK;
     cudaStream_t st = (cudaStream_t)stream;
+    if (p->epilogue == EPI_STORE) return launch<EPI_STORE>(*p, n_blocks, st);
     return p->epilogue == EPI_SWIGLU ? launch<EPI_SWIGLU>(*p, n_blocks, st) : launch<EPI_ADD_F32>(*p, n_blocks, st);
 }

@@ -328,7 +328,7 @@ SPITE_API int spite_gemm_tc_pair(const GemmParams* p, int n_pairs, void* stream)
     if (p->group_offsets ? p->n_groups < 1 : p->n_groups != 1) return SPITE_BAD_ARG;
     if (p->n_groups > 1 && p->w_group_stride != (long long)(p->epilogue == EPI_SWIGLU ? 2 : 1) * p->N * p->K)
         return SPITE_UNSUPPORTED;                              // groups must be stacked without gaps
-    if (p->epilogue < 0 || p->epilogue > EPI_SWIGLU) return SPITE_BAD_ARG;
+    if (p->epilogue < 0 || p->epilogue > EPI_SWIGLU || !activation_ok(p)) return SPITE_BAD_ARG;
     // TMA: 16-byte aligned bases and row pitches
     if (p->K % 8 || p->lda % 8 || (((uintptr_t)p->A | (uintptr_t)p->W) & 15)) return SPITE_UNSUPPORTED;
     if (p->M == 0) return SPITE_OK;

@@ -58,6 +58,6 @@ def main(argv=None) -> int:
     if args.page_size < 1 or 64 % args.page_size:
         ap.error("--page-size must divide 64")
     model = Model.from_folder(args.model, dtype=args.dtype, device=args.device)
-    engine = Engine(model, cache_tokens=args.max_tokens, page_size=args.page_size, max_requests=8)
+    engine = Engine(model, cache_tokens=args.max_tokens, page_size=args.page_size, max_requests=4)
     replay(engine, sys.stdin, Path(args.out))
     return 0

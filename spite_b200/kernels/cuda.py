@@ -20,6 +20,7 @@ _STATUS = {-1: "malformed argument", -2: "size not supported by this kernel", -3
 
 EPI_STORE, EPI_STORE_F32, EPI_ADD_F32, EPI_SWIGLU = 0, 1, 2, 3
 _WINDOW = {"full": 0, "chunk": 1, "sliding": 2}
+_ACTIVATION = {None: 0, "relu2": 1}
 
 
 class GemmParams(C.Structure):
@@ -28,7 +29,7 @@ class GemmParams(C.Structure):
                 ("row_scale", C.c_void_p),
                 ("lda", C.c_longlong), ("ldc", C.c_longlong), ("w_group_stride", C.c_longlong),
                 ("n_groups", C.c_int), ("M", C.c_int), ("N", C.c_int), ("K", C.c_int),
-                ("epilogue", C.c_int), ("scale_by_a_row", C.c_int)]
+                ("epilogue", C.c_int), ("scale_by_a_row", C.c_int), ("activation", C.c_int)]
 
 
 class StepTokens(C.Structure):
@@ -51,7 +52,8 @@ class QkPrepareParams(C.Structure):
 
 class AttentionParams(C.Structure):
     _fields_ = [("q", C.c_void_p), ("out", C.c_void_p), ("num_heads", C.c_int),
-                ("window_kind", C.c_int), ("window_size", C.c_int), ("softmax_scale", C.c_float)]
+                ("window_kind", C.c_int), ("window_size", C.c_int), ("softmax_scale", C.c_float),
+                ("has_sink", C.c_int), ("sink_logit", C.c_float)]
 
 
 class AttnMmaExtra(C.Structure):
@@ -275,15 +277,39 @@ class CudaKernels(KernelSet):
         return t
 
     # ------------------------------------------------------------------ elementwise
-    def embed(self, table, token_ids, out_h, *, scale=1.0):
+    def embed(self, table, token_ids, out_h, *, scale=1.0, position_table=None, positions=None):
         self._t(table, self.dtype, "table"); self._t(token_ids, torch.int32, "token_ids")
         self._t(out_h, torch.float32, "out_h")
         V, d = table.shape
+        if position_table is not None:
+            self._t(position_table, self.dtype, "position_table"); self._t(positions, torch.int32, "positions")
+            if position_table.shape[1] != d or positions.numel() != token_ids.numel():
+                raise KernelError("embed: the position table or the positions do not fit")
+            st = self._lib("elementwise").spite_embed_positions(
+                self._dt, C.c_void_p(table.data_ptr()), C.c_void_p(token_ids.data_ptr()),
+                C.c_void_p(position_table.data_ptr()), C.c_void_p(positions.data_ptr()), C.c_void_p(out_h.data_ptr()),
+                token_ids.numel(), d, V, position_table.shape[0], C.c_float(scale), self._stream())
+            self._count("elementwise", 1)
+            _check(st, "embed (with positions)")
+            return
         st = self._lib("elementwise").spite_embed(
             self._dt, C.c_void_p(table.data_ptr()), C.c_void_p(token_ids.data_ptr()),
             C.c_void_p(out_h.data_ptr()), token_ids.numel(), d, V, C.c_float(scale), self._stream())
         self._count("elementwise", 1)
         _check(st, "embed")
+
+    def pack_pair(self, a, b, out, *, refill=None):
+        self._t(a, torch.float32, "a"); self._t(b, torch.float32, "b"); self._t(out, self.dtype, "out")
+        M, d = a.shape
+        if tuple(b.shape) != (M, d) or tuple(out.shape) != (M, 2 * d):
+            raise KernelError("pack_pair: shapes do not fit")
+        if refill is not None and (self._t(refill, torch.float32, "refill").numel() != d):
+            raise KernelError("pack_pair: the refill vector must have the streams' width")
+        st = self._lib("elementwise").spite_pack_pair(
+            self._dt, C.c_void_p(a.data_ptr()), C.c_void_p(b.data_ptr()), C.c_void_p(_ptr(refill)),
+            C.c_void_p(out.data_ptr()), M, d, self._stream())
+        self._count("elementwise", 1)
+        _check(st, "pack_pair")
 
     def transform_logits(self, logits, *, scale=1.0, softcap=None):
         self._t(logits, torch.float32, "logits")
@@ -400,7 +426,7 @@ class CudaKernels(KernelSet):
         1,905/2,006 at 8,192.  So: gate/up up to 64 rows a group on average, the down product only with
         many groups of 32 to 64 rows."""
         avg = p.M / p.n_groups
-        if p.epilogue == EPI_SWIGLU:
+        if p.epilogue == EPI_SWIGLU or (p.epilogue == EPI_STORE and p.row_scale):     # an expert's first product
             return avg <= self.tc_experts_max_group_rows
         if p.epilogue == EPI_ADD_F32:
             return p.n_groups >= self.tc_experts_down_min_groups and 32 <= avg <= self.tc_experts_max_group_rows
@@ -466,7 +492,7 @@ class CudaKernels(KernelSet):
         words[5] = 0
         return code
 
-    def linear(self, x, w, out, *, accumulate=False, row_scale=None):
+    def linear(self, x, w, out, *, accumulate=False, row_scale=None, activation=None):
         self._t(x, self.dtype, "x"); self._t(w, self.dtype, "w"); self._t(out, None, "out")
         M, K = x.shape
         N = w.shape[0]
@@ -482,9 +508,11 @@ class CudaKernels(KernelSet):
             epi = EPI_STORE
         else:
             raise KernelError(f"linear: output type {out.dtype} not supported")
+        if activation not in _ACTIVATION or (activation is not None and epi != EPI_STORE):
+            raise KernelError(f"linear: activation {activation!r} needs a plain store in the activation type")
         p = GemmParams(A=x.data_ptr(), W=w.data_ptr(), C=out.data_ptr(), a_rows=None, c_rows=None,
                        group_offsets=None, row_scale=_ptr(row_scale), lda=K, ldc=N, w_group_stride=0,
-                       n_groups=1, M=M, N=N, K=K, epilogue=epi, scale_by_a_row=0)
+                       n_groups=1, M=M, N=N, K=K, epilogue=epi, scale_by_a_row=0, activation=_ACTIVATION[activation])
         self._gemm(p, "linear", M)
 
     def linear_swiglu(self, x, w_gate_up, out, *, row_scale=None):
@@ -511,6 +539,22 @@ class CudaKernels(KernelSet):
                        row_scale=_ptr(row_scale), lda=K, ldc=F, w_group_stride=F2 * K,
                        n_groups=E, M=M, N=F, K=K, epilogue=EPI_SWIGLU, scale_by_a_row=1)
         self._gemm(p, "grouped_linear_swiglu", M, gather_src=x)
+
+    def grouped_linear_act(self, x, w_up, sorted_rows, offsets, row_scale, out, *, activation="relu2"):
+        self._t(x, self.dtype, "x"); self._t(w_up, self.dtype, "w"); self._t(out, self.dtype, "out")
+        self._t(sorted_rows, torch.int32, "sorted_rows"); self._t(offsets, torch.int32, "offsets")
+        M, K = x.shape
+        E, F, K2 = w_up.shape
+        if K2 != K or tuple(out.shape) != (M, F) or offsets.numel() != E + 1 or sorted_rows.numel() != M:
+            raise KernelError("grouped_linear_act: shapes do not fit")
+        if activation not in _ACTIVATION:
+            raise KernelError(f"grouped_linear_act: unknown activation {activation!r}")
+        p = GemmParams(A=x.data_ptr(), W=w_up.data_ptr(), C=out.data_ptr(),
+                       a_rows=sorted_rows.data_ptr(), c_rows=None, group_offsets=offsets.data_ptr(),
+                       row_scale=_ptr(row_scale), lda=K, ldc=F, w_group_stride=F * K,
+                       n_groups=E, M=M, N=F, K=K, epilogue=EPI_STORE, scale_by_a_row=1,
+                       activation=_ACTIVATION[activation])
+        self._gemm(p, "grouped_linear_act", M, gather_src=x)
 
     def grouped_linear_accumulate(self, a, w_down, sorted_rows, offsets, h):
         self._t(a, self.dtype, "a"); self._t(w_down, self.dtype, "w"); self._t(h, torch.float32, "h")
@@ -564,11 +608,14 @@ class CudaKernels(KernelSet):
         self._count("attention", 1)
         _check(st, "qk_prepare")
 
-    def paged_attention(self, q, out, batch, cache, *, num_heads, window, softmax_scale, cache_settled=False):
+
+    def paged_attention(self, q, out, batch, cache, *, num_heads, window, softmax_scale, cache_settled=False,
+                        sink_logit=None):
         self._t(q, self.dtype, "q"); self._t(out, self.dtype, "out")
         p = AttentionParams(q=q.data_ptr(), out=out.data_ptr(), num_heads=num_heads,
                             window_kind=_WINDOW[window.kind], window_size=int(window.size),
-                            softmax_scale=float(softmax_scale))
+                            softmax_scale=float(softmax_scale), has_sink=int(sink_logit is not None),
+                            sink_logit=float(sink_logit or 0.0))
         b, c = self._step_tokens(batch, cache.group), self._paged(cache)
         group = num_heads // c.num_kv_heads
         if (self.dtype == torch.bfloat16 and c.head_dim % 16 == 0 and c.head_dim <= 128 and group <= 16

@@ -82,11 +82,15 @@ def relu2_expert(h, w_up, w_down):
     return (z * z) @ w_down.T
 
 
-def moe_ff(h, w_router, experts, top, shared):
+def moe_ff(h, w_router, experts, top, shared, margins=None):
     """Sigmoid scores; the `top` largest are chosen; a chosen expert runs on score * h (the score is
-    not renormalised and multiplies the expert's input); a shared expert runs on h itself."""
+    not renormalised and multiplies the expert's input); a shared expert runs on h itself.
+    `margins`, a list, receives per token the gap between the last chosen logit and the best one left out."""
     z = h.to(torch.float32) @ w_router.to(torch.float32).T
     s = torch.sigmoid(z).to(h.dtype)
+    if margins is not None and z.shape[1] > top:
+        zs = torch.sort(z, dim=-1, descending=True).values
+        margins.append(zs[:, top - 1] - zs[:, top])
     out = torch.zeros_like(h)
     order = torch.argsort(-s, dim=-1, stable=True)[:, :top]
     for t in range(h.shape[0]):
@@ -118,8 +122,10 @@ def layer_order(cfg):
     return order
 
 
-def forward(cfg, w, tokens, dtype=torch.float32, return_layers=False):
-    """Logits [T, vocab] of one whole sequence (and the residual stream after every layer run)."""
+def forward(cfg, w, tokens, dtype=torch.float32, return_layers=False, collect=None):
+    """Logits [T, vocab] of one whole sequence (and the residual stream after every layer run).
+    `collect`, a dict, receives "router_margins" [routed layer runs, T]."""
+    margins = [] if collect is not None else None
     W = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in w.items()}
     eps = float(cfg["norm"]["eps"])
     x = embedding(tokens, W["embed"], W.get("pos"), float(cfg["embedding"]["scale"]))
@@ -145,9 +151,22 @@ def forward(cfg, w, tokens, dtype=torch.float32, return_layers=False):
                 E, top = int(mlp["router"]["experts"]), int(mlp["router"]["top"])
                 experts = [(W[f"{p}mlp.e{e}.up"], W[f"{p}mlp.e{e}.down"]) for e in range(E)]
                 shared = (W[p + "mlp.shared.up"], W[p + "mlp.shared.down"]) if mlp.get("shared") else None
-                x = x + moe_ff(h, W[p + "mlp.router"], experts, top, shared)
+                x = x + moe_ff(h, W[p + "mlp.router"], experts, top, shared, margins)
             else:
                 raise ValueError(f"unknown mlp kind {mlp['kind']!r}")
         after.append(x.clone())
     logits = rms_norm(x, W["final.norm"], eps) @ W["embed"].T
+    if collect is not None:
+        collect["router_margins"] = torch.stack(margins) if margins else torch.zeros((0, len(tokens)))
     return (logits, torch.stack(after)) if return_layers else logits
+
+
+def generate_greedy(cfg, w, prompt, n_new, dtype=torch.float32):
+    """`n_new` tokens by argmax (ties to the highest index), recomputing the whole sequence every time."""
+    toks, out = list(prompt), []
+    for _ in range(n_new):
+        row = forward(cfg, w, toks, dtype=dtype)[-1]
+        best = int((row == row.max()).nonzero().max())
+        out.append(best)
+        toks.append(best)
+    return out

@@ -76,7 +76,8 @@ def test_the_experts_product_refuses_malformed_calls(libs):
         return p, keep
     for kw, want in ((dict(A=None), BAD_ARG), (dict(W=None), BAD_ARG), (dict(C=None), BAD_ARG), (dict(group_offsets=None), BAD_ARG),
                      (dict(n_groups=0), BAD_ARG), (dict(N=0), BAD_ARG), (dict(K=0), BAD_ARG), (dict(lda=8), BAD_ARG),
-                     (dict(epilogue=7), BAD_ARG), (dict(epilogue=0), UNSUPPORTED), (dict(K=100, lda=100), UNSUPPORTED),
+                     (dict(epilogue=7), BAD_ARG), (dict(epilogue=1), UNSUPPORTED), (dict(K=100, lda=100), UNSUPPORTED),
+                     (dict(activation=1), BAD_ARG), (dict(activation=7), BAD_ARG),      # an activation goes with the plain store only
                      (dict(w_group_stride=5), UNSUPPORTED), (dict(n_groups=4000), UNSUPPORTED)):
         p, keep = case(**kw)
         assert lib.spite_gemm_tc_experts(C.byref(p), 148, None) == want, kw
