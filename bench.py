@@ -12,6 +12,8 @@ Two further workloads print a line of the same kind (they are extra modes; the d
                                          # 64 requests with prompts of 16 to 4,096 tokens through the scheduler
     python bench.py --config long        # Scout layer shapes, 8 layers: a prompt of 131,072 tokens in portions of
                                          # 8,192, then 256 decode steps at batch 1 and at batch 4
+    python bench.py --config sezazen     # the Sezazen design beside Llama 4 at equal layer sizes (three sizes): prefill
+                                         # of 2,048 tokens and decode at batch 1 and 8, each with its roofline fraction
 """
 from __future__ import annotations
 
@@ -287,6 +289,152 @@ def run_long(args):
     print(json.dumps(line))
 
 
+# Layer sizes for the comparison of designs: (name, width, query heads, kv heads, key size, value size, experts,
+# experts a token, expert width, shared width, dense width, vocabulary)
+DESIGN_SIZES = [
+    ("small", 2048, 16, 4, 128, 128, 32, 2, 1024, 2048, 8192, 32768),
+    ("medium", 4096, 32, 8, 128, 128, 16, 2, 2048, 4096, 14336, 65536),
+    ("medium, value heads of 96", 4096, 32, 8, 128, 96, 16, 2, 2048, 4096, 14336, 65536),
+]
+
+
+def design_configs(size, runs=8):
+    """A Sezazen model (one dense layer, a loop of two mixture-of-experts layers run three times, one more such
+    layer: eight layer runs) and a Llama 4 model of eight layers with the same widths, heads and experts."""
+    name, d, nq, nkv, kd, vd, E, top, f, fs, fd, V = size
+    mixer = {"heads": nq, "kv_heads": nkv, "dim": kd, "vdim": vd, "scale": kd ** -0.5}
+    moe = {"kind": "moe", "expert": {"ff": f}, "router": {"experts": E, "top": top}, "shared": {"ff": fs}}
+    sez = {"architecture": "Sezazen", "vocab": V, "width": d, "max_positions": 8192, "norm": {"eps": 1e-5},
+           "embedding": {"scale": 1.0}, "loop": {"start": 1, "stop": 3, "times": 3},
+           "layers": [{"type": "attention", "mixer": mixer, "mlp": {"kind": "dense", "ff": fd}}] +
+                     [{"type": "attention", "mixer": mixer, "mlp": moe} for _ in range(3)]}
+    llama = dict(SCOUT, num_hidden_layers=runs, hidden_size=d, num_attention_heads=nq, num_key_value_heads=nkv,
+                 head_dim=kd, num_local_experts=E, num_experts_per_tok=top, intermediate_size=f,
+                 intermediate_size_mlp=fd, moe_layers=list(range(1, runs)), vocab_size=V, tie_word_embeddings=True,
+                 max_position_embeddings=8192)
+    return sez, llama
+
+
+def design_work(model, T, contexts):
+    """(flops of a prompt of T tokens, bytes a decode step over `contexts` must read), from the parts' own sizes
+    as the design states them (no padding): every layer run reads its weights once; experts by the tokens' draw."""
+    from spite_b200.config.specs import LayerCall
+    from spite_b200.parts.feedforward import MoESigmoidPrescaled
+    es, p = 2, model.plan
+    flops, nbytes = 2 * p.hidden_size * p.vocab_size, p.vocab_size * p.hidden_size * es
+    for j in model.junctions:
+        n = sum(1 for c in p.order if not isinstance(c, LayerCall))
+        flops += n * 2 * T * 2 * j.d * j.d
+        nbytes += n * 2 * j.d * j.d * es
+    for call in p.layer_calls():
+        blk = model.blocks[call.layer]
+        m, d = blk.mixer, p.hidden_size
+        w = d * (m.nq * m.kd + m.nkv * m.kd + m.nkv * m.vd) + m.nq * m.vd * d
+        flops += 2 * T * w + 2 * m.nq * (m.kd + m.vd) * T * (T + 1) // 2
+        nbytes += w * es + sum(c * m.nkv * (m.kd + m.vd) * es for c in contexts)
+        f = blk.ffn
+        if f is None:
+            continue
+        if isinstance(f, MoESigmoidPrescaled):
+            mats = 3 if f.gated else 2
+            used = torch_unique(f)
+            flops += 2 * T * d * (f.E + mats * (f.top_k * f.f + f.fs))
+            nbytes += (mats * d * (used * f.f + f.fs)) * es + f.E * d * 4
+        else:
+            flops += 2 * T * 3 * d * f.f
+            nbytes += 3 * d * f.f * es
+    return flops, nbytes
+
+
+def torch_unique(ffn):
+    import torch
+    r = getattr(ffn, "last_routing", None)
+    return int(torch.unique(r.expert_ids).numel()) if r is not None else ffn.E
+
+
+def run_sezazen(args):
+    """The Sezazen design beside the closest existing one, Llama 4, at equal layer sizes: prefill of 2,048 tokens
+    (a fraction of the sustained bf16 rate) and decode at batch 1 and 8 with 2,048 cached tokens (a fraction of
+    the copy bandwidth).  One JSON line; `value` is Sezazen's decode rate at batch 8 at the first size."""
+    import torch
+    from spite_b200.config import config_from_dict
+    from spite_b200.engine import Engine, Model, StepEntry
+    from spite_b200.kernels import build as kb
+    torch.cuda.set_device(0)
+    pk, pk_src = peaks()
+    T, C, steps, warmup = 2048, 2048, max(args.steps, 16), max(args.warmup, 3)
+    out, launches, clocks = {}, 0, ClockSampler()
+
+    def measure(cfgd):
+        nonlocal launches
+        cfg = config_from_dict(cfgd)
+        model = Model.from_config(cfg, dtype="bfloat16", device="cuda:0")
+        kb.ensure_built(model.kernel_libraries() + ["sampling"])
+        model.init_random(seed=0, std=0.02)
+        ks, V = model.kernels, model.plan.vocab_size
+        engine = Engine(model, cache_tokens=9 * (C + 256), page_size=64, max_requests=9)
+        g = torch.Generator().manual_seed(5)
+        res = {}
+        # prefill: one prompt of T tokens, its last position's logits; a new request every time
+        ms = []
+        for i in range(warmup + 5):
+            toks = torch.randint(0, V, (T,), generator=g).tolist()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            engine.step([StepEntry("p", toks, [T - 1])])
+            e1.record()
+            torch.cuda.synchronize()
+            engine.finish("p")
+            if i >= warmup:
+                ms.append(e0.elapsed_time(e1))
+        pre = sorted(ms)[len(ms) // 2]
+        flops, _ = design_work(model, T, [])
+        res.update(prefill_ms=round(pre, 3), prefill_tok_s=round(T * 1e3 / pre), prefill_tflops=round(flops / pre / 1e9, 1),
+                   prefill_frac=round(flops / (pre * 1e-3) / (pk["bf16_tflops_sustained"] * 1e12), 3))
+        for B in (1, 8):
+            rids = [f"d{B}_{i}" for i in range(B)]
+            for r in rids:
+                engine.step([StepEntry(r, torch.randint(0, V, (C,), generator=g).tolist(), [])])
+            ids = torch.randint(0, V, (steps + warmup, B), generator=g).tolist()
+            for i in range(warmup):
+                ks.argmax(engine.step([StepEntry(r, [ids[i][j]], [0]) for j, r in enumerate(rids)]))
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for i in range(warmup, warmup + steps):
+                ks.argmax(engine.step([StepEntry(r, [ids[i][j]], [0]) for j, r in enumerate(rids)]))
+            e1.record()
+            torch.cuda.synchronize()
+            dms = e0.elapsed_time(e1) / steps
+            _, nbytes = design_work(model, 1, [engine.cached_tokens(r) for r in rids])
+            res.update({f"decode_b{B}_ms": round(dms, 4), f"decode_b{B}_tok_s": round(B * 1e3 / dms, 1),
+                        f"decode_b{B}_gb": round(nbytes / 1e9, 3),
+                        f"decode_b{B}_hbm_frac": round(nbytes / (dms * 1e-3) / (pk["hbm_gbs"] * 1e9), 3)})
+            for r in rids:
+                engine.finish(r)
+        engine.check()
+        launches += ks.launches
+        res["weights_gb"] = round(model.weight_bytes() / 1e9, 2)
+        del engine, model
+        torch.cuda.empty_cache()
+        return res
+
+    with clocks:
+        for size in DESIGN_SIZES:
+            sez, llama = design_configs(size)
+            out[size[0]] = {"sezazen": measure(sez), "llama4": measure(llama)}
+    first = out[DESIGN_SIZES[0][0]]["sezazen"]
+    line = base_line("decode tok/s at batch 8, context 2,048 (Sezazen design, first size)", first["decode_b8_tok_s"], "tok/s",
+                     steps, warmup, first["decode_b8_ms"],
+                     {"model": "sezazen beside llama4 at equal layer sizes", "layer_runs": 8, "prefill_tokens": T, "context": C,
+                      "sizes": {s[0]: dict(zip(("width", "q_heads", "kv_heads", "key_dim", "value_dim", "experts", "top", "expert_ff",
+                                                "shared_ff", "dense_ff", "vocab"), s[1:])) for s in DESIGN_SIZES},
+                      "global_batch": 8, "seq_len": C, "page_size": 64, "parallelism": "single-gpu",
+                      "l2": "inputs larger than L2 (the weights a step reads exceed 126 MB)"})
+    line.update({"gpu_launches": launches, "clocks": clocks.summary(), "peaks": dict(pk, source=pk_src), "designs": out})
+    print(json.dumps(line))
+
+
 def run_ours(args):
     import torch
     from spite_b200.engine import Engine, StepEntry
@@ -481,8 +629,8 @@ def main(argv=None):
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--config", choices=["scout", "maverick", "long"], default="scout",
-                    help="scout: the benchmark line; maverick, long: two further workloads, one line each")
+    ap.add_argument("--config", choices=["scout", "maverick", "long", "sezazen"], default="scout",
+                    help="scout: the benchmark line; maverick, long, sezazen: further workloads, one line each")
     ap.add_argument("--layers", type=int, default=FULL_LAYERS)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=8192)
@@ -502,6 +650,9 @@ def main(argv=None):
         return 0
     if args.config == "long":
         run_long(args)
+        return 0
+    if args.config == "sezazen":
+        run_sezazen(args)
         return 0
     if args.warmup < 3:
         args.warmup = 3

@@ -7,10 +7,13 @@ peak.  Also the small driver that `ncu` captures for the summaries under `profil
     python bench_kernels.py --small              # shapes a profiler can replay in seconds
     python bench_kernels.py --only gemm_decode --case "lm_head M=8"   # one case
     python bench_kernels.py --only gemm_decode,moe_decode --rows 4,6   # the decode families at other token counts
+    python bench_kernels.py --only attention_decode,attention_prefill --sink 0   # attention with a sink in the softmax
+    python bench_kernels.py --only gated_less    # experts without a gate (squared ReLU), the junction of a loop,
+                                                 # the embedding with learned positions
 
 Families: gemm_decode (weight streaming, mma.sync), gemm_prefill (tcgen05/TMA),
 moe_decode, moe_prefill (grouped products), attention_decode, attention_prefill,
-small (norm, rotation + cache append, router, sampling).
+small (norm, rotation + cache append, router, sampling), gated_less (what the Sezazen design adds).
 """
 from __future__ import annotations
 
@@ -38,6 +41,7 @@ def main(argv=None):
     ap.add_argument("--case", default="", help="run only the cases whose name contains this text")
     ap.add_argument("--experts", type=int, default=16, help="experts of the grouped products (128: Maverick's)")
     ap.add_argument("--rows", default="1,8,64", help="token counts of the decode families")
+    ap.add_argument("--sink", type=float, default=None, help="attention cases run with a sink of this score in the softmax")
     args = ap.parse_args(argv)
     dev = "cuda:0"
     torch.cuda.set_device(0)
@@ -171,8 +175,40 @@ def main(argv=None):
                    nbytes=used * 2 * F * d, flops=2 * M * F * d)
         del w_gu, w_dn
 
+    # ---- what a design without gates in its experts adds: the experts' first product with relu(y)^2 in its epilogue
+    # (beside the gated one above: half the weight rows), the junction of a loop, the embedding with learned positions
+    if want("gated_less"):
+        w_up, w_s = rnd(E, F, d), rnd(F, d)
+        for M in decode_rows + ((512,) if args.small else (512, 2048)):
+            rows, offsets, used = routed(M)
+            used = E if M > 64 else used
+            x, scale = rnd(M, d), torch.rand(M, device=dev)
+            a = torch.empty((M, F), dtype=bf, device=dev)
+            report("gated_less", f"experts_up_relu2 M={M} experts_used={used}",
+                   timed(lambda: ks.grouped_linear_act(x, w_up, rows, offsets, scale, a, activation="relu2")),
+                   nbytes=used * 2 * F * d, flops=2 * M * F * d)
+            report("gated_less", f"shared_up_relu2 M={M} N={F} K={d}",
+                   timed(lambda: ks.linear(x, w_s, a, activation="relu2")), nbytes=2 * F * d, flops=2 * M * F * d)
+            report("gated_less", f"shared_up_plain_store M={M} N={F} K={d}",
+                   timed(lambda: ks.linear(x, w_s, a)), nbytes=2 * F * d, flops=2 * M * F * d)
+        del w_up, w_s
+        for M in (8, 2048):
+            def make_pack(M=M):
+                h, h0, step = torch.randn((M, d), device=dev), torch.randn((M, d), device=dev), torch.randn(d, device=dev)
+                x = torch.empty((M, 2 * d), dtype=bf, device=dev)
+                return lambda: ks.pack_pair(h, h0, x, refill=step)
+            report("gated_less", f"pack_pair M={M}", timed_rotating(make_pack, max(M * d * 16, 64 << 20)), nbytes=M * d * 16)
+            def make_embed(M=M):
+                table, pos_t = rnd(V, d), rnd(8192, d)
+                toks = torch.randint(0, V, (M,), dtype=torch.int32, device=dev)
+                pos = torch.arange(M, dtype=torch.int32, device=dev)
+                h = torch.empty((M, d), dtype=torch.float32, device=dev)
+                return lambda: ks.embed(table, toks, h, scale=2.0, position_table=pos_t, positions=pos)
+            report("gated_less", f"embed_positions M={M}", timed(make_embed()), nbytes=M * d * 8)
+
     # ---- attention over the paged cache
     P = 64
+    sink = "" if args.sink is None else f" sink={args.sink}"
     def attention_case(fam, n_req, n_new, ctx, window):
         pages_per = -(-ctx // P)
         win = Window(*window)
@@ -187,14 +223,14 @@ def main(argv=None):
             q, out = rnd(off, nq * hd), torch.empty((off, nq * hd), dtype=bf, device=dev)
             cache = LayerCache(0, kv, None, P, False)
             return lambda: ks.paged_attention(q, out, batch, cache, num_heads=nq, window=win,
-                                              softmax_scale=1 / math.sqrt(hd))
+                                              softmax_scale=1 / math.sqrt(hd), sink_logit=args.sink)
         seen = sum(min(p + 1, ctx) - win.lowest_visible(p) for p in range(ctx - n_new, ctx)) / n_new
         if n_new == 1:
             # short launches: back to back over rotating copies of the cache, so no launch gap is counted
             nbytes = int(n_req * seen * 2 * nkv * hd * 2)
-            report(fam, f"requests={n_req} context={ctx} window={window[0]}", timed_rotating(make, nbytes), nbytes=nbytes)
+            report(fam, f"requests={n_req} context={ctx} window={window[0]}{sink}", timed_rotating(make, nbytes), nbytes=nbytes)
             return
-        report(fam, f"tokens={n_new} context={ctx} window={window[0]}", timed(make()),
+        report(fam, f"tokens={n_new} context={ctx} window={window[0]}{sink}", timed(make()),
                flops=int(n_req * n_new * seen * 4 * nq * hd))
     if want("attention_decode"):
         for n_req in ((8,) if args.small else (1, 8, 64)):
