@@ -77,7 +77,7 @@ class PagedAttention(Mixer):
                 raise ConfigError(f"temperature floor_scale {floor} must be a positive integer")
             temperature_tuning = (int(floor), float(scale))
         self.temperature = temperature_tuning
-        self.softmax_scale = float(softmax_scale) if softmax_scale else 1.0 / math.sqrt(self.kd)
+        self.softmax_scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(self.kd)
         self.wqkv = self.wo = None
 
     def param_specs(self):

@@ -385,3 +385,26 @@ def test_trace_replay_program(folder, tmp_path):
             pos[e["id"]] = base + len(e["tokens"])
         assert i == rows.shape[0]
     S.compare_with_plain(got, path, requests, 2e-5)
+
+
+def test_the_command_line_runs_a_sezazen_folder(tmp_path):
+    """`spite random`, `spite run` (greedy, float32: the plain implementation's tokens) and `spite bench`."""
+    import subprocess, sys
+    from pathlib import Path
+    root = Path(__file__).resolve().parent.parent
+    spite = lambda *a: subprocess.run([sys.executable, str(root / "bin" / "spite")] + [str(x) for x in a],
+                                      capture_output=True, text=True, timeout=900)
+    cfg_file = tmp_path / "cfg.json"
+    cfg_file.write_text(json.dumps(S.CONFIG_P))
+    model = tmp_path / "model"
+    assert spite("random", "--config", cfg_file, "--out", model, "--seed", 3, "--std", 0.08).returncode == 0
+    cfg, W = plain.load_folder(model)
+    prompt = H.random_tokens(300, 17, 2)
+    proc = spite("run", "-m", model, "-p", " ".join(map(str, prompt)), "--max-tokens", 6, "--temperature", 0,
+                 "--dtype", "fp32", "--page-size", 16, "--num-pages", 8)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [int(t) for t in proc.stdout.split()] == plain.generate_greedy(cfg, W, prompt, 6)
+    proc = spite("bench", "-m", model, "--n-prompt", 40, "--n-tokens", 12, "--n-runs", 2, "--json", "--dtype", "bf16")
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    report = json.loads(proc.stdout)
+    assert report["decode_tps"] > 0 and report["prefill_tps"] > 0

@@ -163,3 +163,21 @@ def test_a_pass_of_the_loop_does_not_read_another_pass_cache(folders):
     first, second = eng.storage.layer_cache(1, True), eng.storage.layer_cache(3, True)     # layer 1 in pass 0 and in pass 1
     assert first.group == second.group and first.kv.data_ptr() != second.kv.data_ptr()
     assert not torch.equal(first.kv, second.kv)
+
+
+def test_the_command_line_writes_a_random_model_folder(tmp_path):
+    """`spite random` with a Sezazen configuration: experts one tensor each, as the design's files have them."""
+    from spite_b200 import cli
+    from spite_b200.weights import load_bound_tensors
+    cfg_file = tmp_path / "cfg.json"
+    cfg_file.write_text(json.dumps(S.CONFIG_Q))
+    out = tmp_path / "model"
+    assert cli.main(["random", "--config", str(cfg_file), "--out", str(out), "--seed", "4", "--std", "0.05"]) == 0
+    config = load_config(out)
+    assert isinstance(config, SezazenConfig) and config.loop.times == 3
+    _, tensors = plain.load_folder(out)
+    assert sorted(n for n in tensors if n.startswith("l0.mlp.e")) == sorted(f"l0.mlp.e{e}.{w}" for e in range(4) for w in ("up", "down"))
+    assert tuple(tensors["loop.step"].shape) == (3, 128) and tuple(tensors["pos"].shape) == (1024, 128)
+    bound = load_bound_tensors(out, config)
+    assert tuple(bound["layers.0.ffn.experts_up"].shape) == (4, 64, 128)
+    assert tuple(bound["junctions.0.in_proj"].shape) == (128, 256)
