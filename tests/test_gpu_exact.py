@@ -115,7 +115,7 @@ def _cuts(requests):
     m, o = requests["m"], requests["o"]
     portions = []
     i = 0
-    for n in (64, 100, 2, 2):                                        # 64 / 100 / 2 / the rest, as the contract names them
+    for n in (64, 100, 2, 2):                                        # 64 / 100 / 2 / the rest
         portions.append({"entries": [{"id": "m", "tokens": m[i:i + n], "want": list(range(n))}], "end": []})
         i += n
     assert i == len(m)

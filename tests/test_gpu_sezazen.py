@@ -213,6 +213,39 @@ def test_grouped_squared_relu_experts(dtype, M, E, F, K):
     assert not ks.errors()
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("M,d,E,top,f,fs", [(1, 64, 4, 2, 40, 0), (23, 96, 6, 3, 32, 48), (300, 128, 5, 1, 64, 128), (40, 100, 3, 3, 20, 12)])
+def test_the_mixture_of_experts_without_gates_alone(dtype, M, d, E, top, f, fs):
+    """The feed-forward part by itself: sigmoid scores, the `top` largest chosen, the score multiplies the
+    expert's input and is not renormalised, relu(.)^2 between up and down, a shared expert of its own size."""
+    from spite_b200.config import PartSpec
+    from spite_b200.kernels import build
+    from spite_b200.parts import BuildContext, build_part
+    build.ensure_built(["elementwise", "gemm_simt", "gemm_stream", "gemm_skinny", "gemm_tc", "gemm_tc_pair", "gemm_tc_experts", "moe"])
+    ks = kernels(dtype)
+    part = build_part("feed_forward", PartSpec("moe_sigmoid_prescaled", {
+        "hidden_size": d, "num_experts": E, "top_k": top, "expert_size": f, "shared_size": fs, "activation": "relu2"}),
+        BuildContext(ks, dtype, torch.device(DEV)))
+    g = torch.Generator().manual_seed(M + E)
+    params = {n: (torch.randn(s.shape, generator=g) / math.sqrt(s.shape[-1])).to(torch.bfloat16) for n, s in part.param_specs().items()}
+    params["router"] = (params["router"].float() * 6).to(torch.bfloat16)          # scores well apart from one half
+    assert "experts_gate_up" not in params and "shared_gate_proj" not in params
+    part.bind({n: t.to(DEV) for n, t in params.items()})
+    x = torch.randn((M, d), generator=g).to(dtype)
+    if dtype == torch.bfloat16:                              # keep tokens whose choice of experts rounding cannot change
+        z = torch.sort(x.float() @ params["router"].float().T, descending=True).values
+        if E > top:
+            x = x[(z[:, top - 1] - z[:, top]) > 0.05]
+    h = torch.zeros((x.shape[0], d), dtype=torch.float32, device=DEV)
+    part.forward(x.to(DEV), h, None)
+    torch.cuda.synchronize()
+    P = {n: t.double() for n, t in params.items()}
+    experts = [(P["experts_up"][e], P["experts_down"][e]) for e in range(E)]
+    shared = (P["shared_up_proj"], P["shared_down_proj"]) if fs else None
+    ref = plain.moe_ff(x.double(), P["router"], experts, top, shared)
+    close(h, ref, 2e-2 if dtype == torch.bfloat16 else 1e-5, "mixture of experts without gates")
+
+
 # ---------------------------------------------------------------------------- positions and the junction
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_embedding_with_learned_positions(dtype):
