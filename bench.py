@@ -362,7 +362,7 @@ def run_sezazen(args):
     from spite_b200.kernels import build as kb
     torch.cuda.set_device(0)
     pk, pk_src = peaks()
-    T, C, steps, warmup = 2048, 2048, max(args.steps, 16), max(args.warmup, 3)
+    T, C, steps, warmup = 2048, 2048, args.steps if args.only_decode else max(args.steps, 16), max(args.warmup, 3)
     out, launches, clocks = {}, 0, ClockSampler()
 
     def measure(cfgd):
@@ -372,12 +372,13 @@ def run_sezazen(args):
         kb.ensure_built(model.kernel_libraries() + ["sampling"])
         model.init_random(seed=0, std=0.02)
         ks, V = model.kernels, model.plan.vocab_size
-        engine = Engine(model, cache_tokens=9 * (C + 256), page_size=64, max_requests=9)
+        engine = Engine(model, cache_tokens=9 * (C + 256), page_size=64, max_requests=9,
+                        cuda_graphs=False if args.no_graphs else None)
         g = torch.Generator().manual_seed(5)
         res = {}
         # prefill: one prompt of T tokens, its last position's logits; a new request every time
         ms = []
-        for i in range(warmup + 5):
+        for i in range(0 if args.only_decode else warmup + 5):
             toks = torch.randint(0, V, (T,), generator=g).tolist()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
@@ -387,11 +388,14 @@ def run_sezazen(args):
             engine.finish("p")
             if i >= warmup:
                 ms.append(e0.elapsed_time(e1))
-        pre = sorted(ms)[len(ms) // 2]
-        flops, _ = design_work(model, T, [])
-        res.update(prefill_ms=round(pre, 3), prefill_tok_s=round(T * 1e3 / pre), prefill_tflops=round(flops / pre / 1e9, 1),
-                   prefill_frac=round(flops / (pre * 1e-3) / (pk["bf16_tflops_sustained"] * 1e12), 3))
-        for B in (1, 8):
+        if ms:
+            pre = sorted(ms)[len(ms) // 2]
+            flops, _ = design_work(model, T, [])
+            res.update(prefill_ms=round(pre, 3), prefill_tok_s=round(T * 1e3 / pre), prefill_tflops=round(flops / pre / 1e9, 1),
+                       prefill_frac=round(flops / (pre * 1e-3) / (pk["bf16_tflops_sustained"] * 1e12), 3))
+        for B in ((args.batch,) if args.only_decode else (1, 8)):
+            if args.only_prefill:
+                break
             rids = [f"d{B}_{i}" for i in range(B)]
             for r in rids:
                 engine.step([StepEntry(r, torch.randint(0, V, (C,), generator=g).tolist(), [])])
@@ -419,13 +423,16 @@ def run_sezazen(args):
         torch.cuda.empty_cache()
         return res
 
+    sizes = [s for s in DESIGN_SIZES if args.size in (None, s[0])]
     with clocks:
-        for size in DESIGN_SIZES:
+        for size in sizes:
             sez, llama = design_configs(size)
-            out[size[0]] = {"sezazen": measure(sez), "llama4": measure(llama)}
-    first = out[DESIGN_SIZES[0][0]]["sezazen"]
-    line = base_line("decode tok/s at batch 8, context 2,048 (Sezazen design, first size)", first["decode_b8_tok_s"], "tok/s",
-                     steps, warmup, first["decode_b8_ms"],
+            out[size[0]] = {name: measure(cfgd) for name, cfgd in (("sezazen", sez), ("llama4", llama))
+                            if args.design in ("both", name)}
+    first = next(iter(out[sizes[0][0]].values()))
+    key = f"decode_b{args.batch if args.only_decode else 8}"
+    line = base_line("decode tok/s at batch 8, context 2,048 (Sezazen design, first size)", first.get(key + "_tok_s", 0.0), "tok/s",
+                     steps, warmup, first.get(key + "_ms", 0.0),
                      {"model": "sezazen beside llama4 at equal layer sizes", "layer_runs": 8, "prefill_tokens": T, "context": C,
                       "sizes": {s[0]: dict(zip(("width", "q_heads", "kv_heads", "key_dim", "value_dim", "experts", "top", "expert_ff",
                                                 "shared_ff", "dense_ff", "vocab"), s[1:])) for s in DESIGN_SIZES},
@@ -639,6 +646,8 @@ def main(argv=None):
     ap.add_argument("--only-decode", action="store_true", help="measure the decode step only (for profiling)")
     ap.add_argument("--only-prefill", action="store_true", help="measure the prefill step only (for profiling)")
     ap.add_argument("--verbose", action="store_true", help="print the single prefill timings to standard error")
+    ap.add_argument("--size", default=None, help="--config sezazen: only this set of layer sizes (small, medium, ...)")
+    ap.add_argument("--design", choices=["both", "sezazen", "llama4"], default="both", help="--config sezazen: only this design")
     args = ap.parse_args(argv)
     if args.impl == "reference":
         return run_reference(args)
