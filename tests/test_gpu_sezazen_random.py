@@ -102,3 +102,17 @@ def test_the_drawn_configurations_differ(tmp_path):
     kinds = [json.dumps(random_config(s), sort_keys=True) for s in range(10)]
     assert len(set(kinds)) == 10
     assert any("loop" not in json.loads(k) for k in kinds) and any(json.loads(k).get("loop", {}).get("start") == 0 for k in kinds)
+
+
+def test_bfloat16_long_prompt(model_folder):
+    """A prompt of several hundred tokens (several 128-row tiles of the prompt kernels, keys hundreds of positions
+    back, key splits in decoding) in bfloat16: whole, its last 40 tokens decoded, and in portions."""
+    from spite_b200.engine import Model
+    folder, cfg, seed = model_folder
+    if seed not in (0, 8):
+        pytest.skip("long prompts for two of the configurations")
+    model = Model.from_folder(folder, dtype="bfloat16", device=DEV)
+    reqs = {"long": S.decisive_tokens(folder, 300, seed + 100, 0.04)}
+    for steps, page in ((H.steps_whole(reqs), 64), (H.steps_last_decoded(reqs, 40), 64),
+                        (H.steps_portions(reqs, seed=seed, sizes=(2, 17, 64, 150)), 64)):
+        S.compare_with_plain(_run(model, steps, page), folder, reqs, 2.5e-2)
