@@ -256,5 +256,13 @@ class SezazenConfig:
         out.append(B("final_norm.weight", "final.norm", (d,), init="ones"))
         return out
 
+    def unused_tensor_names(self) -> set:
+        """What a file may carry for parts this configuration switches off: the second norm of a layer without a
+        feed-forward, the loop's tensors of a model without a loop."""
+        names = {f"l{i}.norm2" for i, L in enumerate(self.layers) if L.mlp is None}
+        if self.loop is None:
+            names |= {"loop.in", "loop.step"}
+        return names
+
     checkpoint_prefixes = ("",)
     ignored_prefixes = ()

@@ -69,6 +69,13 @@ def _sources(binding) -> tuple:
     return (src,) if isinstance(src, str) else tuple(src)
 
 
+def _unused_names(config) -> set:
+    """Tensors a file of this configuration may hold although the model does not use them (`config.unused_tensor_names()`,
+    optional): they are passed over in silence instead of being reported as unexpected."""
+    fn = getattr(config, "unused_tensor_names", None)
+    return set(fn()) if fn else set()
+
+
 def apply_binding(binding, tensor, device="cpu"):
     """The parameter that `binding` makes of the checkpoint tensor `tensor` (a list of tensors for a binding
     that stacks several)."""
@@ -96,7 +103,8 @@ def bind_tensors(config, source: dict, device="cpu", folder="(tensors in memory)
              if n in source and tuple(source[n].shape) != tuple(b.source_shape)]
     used = {n for _, n in named}
     ignored = tuple(getattr(config, "ignored_prefixes", ()))
-    unexpected = sorted(n for n in source if n not in used and not (ignored and n.startswith(ignored)))
+    unused = _unused_names(config)
+    unexpected = sorted(n for n in source if n not in used and n not in unused and not (ignored and n.startswith(ignored)))
     if missing or wrong or unexpected:
         raise WeightError(folder, missing, wrong, unexpected)
     return {b.target: apply_binding(b, source[b.source] if isinstance(b.source, str) else
@@ -138,7 +146,8 @@ def load_bound_tensors(folder, config, device="cpu") -> dict[str, torch.Tensor]:
                 got = where[name].entries[name][1]
                 if tuple(got) != tuple(b.source_shape):
                     wrong.append((name, got, b.source_shape))
-        unexpected = sorted(n for n in where if n not in used and not (ignored and n.startswith(ignored)))
+        unused = {prefix + n for n in _unused_names(config)}
+        unexpected = sorted(n for n in where if n not in used and n not in unused and not (ignored and n.startswith(ignored)))
         if missing or wrong or unexpected:
             raise WeightError(folder, missing, wrong, unexpected)
         out = {}

@@ -89,6 +89,8 @@ def test_experts_stored_one_by_one_are_stacked_and_a_missing_one_is_listed():
         assert torch.equal(up[e], tensors[f"l1.mlp.e{e}.up"])
     assert torch.equal(bound["layers.3.ffn.experts_down"][4], tensors["l3.mlp.e4.down"])
     assert "layers.2.ffn_norm.weight" not in bound and "layers.3.ffn.shared_up_proj" not in bound
+    tensors["l2.norm2"] = torch.ones(64)                  # the norm of a feed-forward the layer does not have: passed over
+    assert set(bind_tensors(cfg, tensors)) == set(bound)
     del tensors["l1.mlp.e4.down"]
     tensors["l3.mlp.e1.up"] = tensors["l3.mlp.e1.up"][:, :10]
     tensors["l9.norm1"] = torch.ones(64)
