@@ -2,7 +2,7 @@
 
 The file describes the model layer by layer: `layers[i]` gives the layer's `type` (its mixer), the
 mixer's sizes (`mixer`) and its feed-forward (`mlp`, or null for none); `loop` names a range of layers
-that runs several times in a row with the same weights; `embedding.scale`, `norm.eps`, `vocab`, `width`
+whose layers are applied repeatedly (one set of weights, several passes); `embedding.scale`, `norm.eps`, `vocab`, `width`
 and `max_positions` are the model's own.  Every size and every constant that the file gives is read
 from it; what the design fixes (the sink's score of zero, the squared-ReLU experts, the tied output
 head, the learned position vectors) is stated in `plan()`.
@@ -19,7 +19,7 @@ from typing import Optional
 from .registry import register_architecture
 from .specs import BlockSpec, ConfigError, JunctionCall, LayerCall, ModelPlan, PartSpec, WeightBinding
 
-#: score of the key without a value that every softmax of the design holds: one is added to the denominator
+#: every softmax of the design has a sink of this score: exp(0) = 1 joins the sum of exponentials
 SINK_LOGIT = 0.0
 
 

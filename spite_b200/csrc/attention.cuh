@@ -55,7 +55,7 @@ struct AttentionParams {
     int window_size;
     float softmax_scale;
     int has_sink;               // the softmax's denominator also holds exp(sink_logit): a key every query sees
-    float sink_logit;           // and that has no value (with 0: one is added to the denominator)
+    float sink_logit;           // and that adds nothing to the output (a score of 0 puts exp(0) = 1 into the sum)
 };
 
 // The sink folded into a finished softmax state: `m` and `l` are the maximum and the sum of exp(s - m) over the

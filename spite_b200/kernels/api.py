@@ -51,7 +51,7 @@ class KernelSet:
     # ---- elementwise
     def embed(self, table, token_ids, out_h, *, scale=1.0, position_table=None, positions=None):
         """out_h[m, :] (float32) = table[token_ids[m], :] (T) * scale; with a `position_table` [P, d] (T)
-        and `positions` [M] int32, + position_table[positions[m], :] (not scaled)."""
+        and `positions` [M] int32, + position_table[positions[m], :] (the factor applies to the token's row only)."""
         raise NotImplementedError
 
     def pack_pair(self, a, b, out, *, refill=None):

@@ -4,7 +4,7 @@ One part serves every attention layer: the window rule (all keys, the keys of
 the query's chunk, the last W keys), the position encoding, the per-head norm of
 q and k (after or before the rotation, with gains or without), the
 temperature factor, a value size that differs from the key size, and a sink in
-the softmax (a key of a fixed score that carries no value) are constructor parameters.
+the softmax (an extra term exp(sink) in the sum, with nothing behind it) are constructor parameters.
 
 Formulas: crates/spite-models/src/llama/llama4.rs:126-207 (projections, rotation
 then norm, temperature factor on layers without rotation, append to the cache,
@@ -32,8 +32,8 @@ class PagedAttention(Mixer):
                  qk_norm_before_rotation=False, temperature_tuning=None, softmax_scale=None,
                  value_dim=None, sink_logit=None):
         """`head_dim` is the size of a query and a key head, `value_dim` that of a value head (default: the
-        same).  `sink_logit`, if given, is the score of a key that every query sees and that has no value:
-        p_j = exp(s_j) / (exp(sink) + sum exp(s_j')); with 0 the softmax has one added to its denominator."""
+        same).  `sink_logit`, if given, is the score of a sink: a term exp(sink) in every softmax's sum that adds
+        nothing to the output, p_j = exp(s_j) / (exp(sink) + sum exp(s_j'))."""
         super().__init__(ctx)
         if num_heads % num_kv_heads:
             raise ConfigError(f"{num_heads} query heads cannot share {num_kv_heads} kv heads evenly")

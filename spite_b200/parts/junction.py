@@ -2,7 +2,7 @@
 
 `reinject_linear`: h <- W [h; h0] + b[step].  The stream is mixed with the embedding's output h0 through
 one matrix [d, 2d] (the columns that multiply h first), and a learned vector of the pass is added.  A
-model that runs a range of its layers several times with the same weights puts this before every pass.
+model that applies a range of its layers repeatedly puts this before every pass.
 The product runs in the activation type with float32 sums; the vector and the sum are float32.
 """
 from __future__ import annotations

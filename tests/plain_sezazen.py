@@ -39,12 +39,12 @@ def load_folder(folder):
 
 # ---------------------------------------------------------------------------------- mechanisms
 def rms_norm(x, w, eps):
-    """x / sqrt(mean(x^2) + eps) * w, eps inside the root."""
+    """y = x * w / sqrt(mean(x^2) + eps): the epsilon joins the mean square before the square root is taken."""
     return x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps) * w
 
 
 def embedding(tokens, embed, pos, scale):
-    """embed[token] * scale + pos[p]; positions count from 0 (the position vector is not scaled)."""
+    """x_p = scale * embed[token_p] + pos[p], p = 0, 1, ...: the factor applies to the token's row only."""
     T = len(tokens)
     x = embed[torch.tensor(tokens, dtype=torch.long)] * scale
     if pos is not None:
@@ -53,8 +53,9 @@ def embedding(tokens, embed, pos, scale):
 
 
 def sink_attention(h, wq, wk, wv, wo, heads, kv_heads, dim, vdim, scale):
-    """Causal grouped-query attention without rotation; the softmax has one added to its denominator
-    (a key of score 0 that carries no value):  p_ij = exp(s_ij) / (1 + sum_{j' <= i} exp(s_ij'))."""
+    """Causal grouped-query attention, no rotation of q and k.  Weights
+    p_ij = exp(s_ij) / (1 + sum_{j' <= i} exp(s_ij')): the 1 is exp(0), the share of a sink that contributes nothing
+    to the output, so the weights of a row sum to less than one."""
     T = h.shape[0]
     q = (h @ wq.T).reshape(T, heads, dim)
     k = (h @ wk.T).reshape(T, kv_heads, dim)
@@ -83,8 +84,8 @@ def relu2_expert(h, w_up, w_down):
 
 
 def moe_ff(h, w_router, experts, top, shared, margins=None):
-    """Sigmoid scores; the `top` largest are chosen; a chosen expert runs on score * h (the score is
-    not renormalised and multiplies the expert's input); a shared expert runs on h itself.
+    """s = sigmoid(router logits); the experts with the `top` largest s run, expert e on s_e * h (the raw
+    score scales what goes into the expert; the chosen scores are not made to sum to one); a shared expert runs on h.
     `margins`, a list, receives per token the gap between the last chosen logit and the best one left out."""
     z = h.to(torch.float32) @ w_router.to(torch.float32).T
     s = torch.sigmoid(z).to(h.dtype)

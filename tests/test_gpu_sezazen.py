@@ -216,8 +216,8 @@ def test_grouped_squared_relu_experts(dtype, M, E, F, K):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("M,d,E,top,f,fs", [(1, 64, 4, 2, 40, 0), (23, 96, 6, 3, 32, 48), (300, 128, 5, 1, 64, 128), (40, 100, 3, 3, 20, 12)])
 def test_the_mixture_of_experts_without_gates_alone(dtype, M, d, E, top, f, fs):
-    """The feed-forward part by itself: sigmoid scores, the `top` largest chosen, the score multiplies the
-    expert's input and is not renormalised, relu(.)^2 between up and down, a shared expert of its own size."""
+    """The feed-forward part by itself: sigmoid scores, the `top` largest chosen, expert e fed with s_e * h (raw
+    scores), relu(.)^2 between up and down, a shared expert of its own size."""
     from spite_b200.config import PartSpec
     from spite_b200.kernels import build
     from spite_b200.parts import BuildContext, build_part
@@ -257,7 +257,7 @@ def test_embedding_with_learned_positions(dtype):
     pos = torch.randint(0, 64, (21,), generator=g).to(torch.int32)
     h = torch.empty((21, 100), dtype=torch.float32, device=DEV)
     ks.embed(table.to(DEV), toks.to(DEV), h, scale=2.5, position_table=pos_table.to(DEV), positions=pos.to(DEV))
-    ref = table[toks.long()].double() * 2.5 + pos_table[pos.long()].double()        # the position vector is not scaled
+    ref = table[toks.long()].double() * 2.5 + pos_table[pos.long()].double()        # the factor applies to the token's row only
     close(h, ref, 1e-6, "embedding with positions")
 
 
