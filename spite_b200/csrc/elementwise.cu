@@ -20,8 +20,15 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
     for (int i = threadIdx.x; i < d; i += blockDim.x) out[i] = to_f32(row[i]) * scale;
 }
 
-// h[m, :] = table[token[m], :] * scale + pos_table[positions[m], :]: learned position vectors, added unscaled;
-// the sum is float32
+// Four elements with one store.
+__device__ __forceinline__ void store4(float* p, float a, float b, float c, float d) { *(float4*)p = make_float4(a, b, c, d); }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, float a, float b, float c, float d) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    *(uint2*)p = make_uint2(*(unsigned*)&lo, *(unsigned*)&hi);
+}
+
+// h[m, :] = table[token[m], :] * scale + pos_table[positions[m], :]: learned position vectors (the factor applies to the
+// token's row only); the sum is float32
 template <typename T>
 __global__ void embed_positions_kernel(const T* __restrict__ table, const int* __restrict__ tokens,
                                        const T* __restrict__ pos_table, const int* __restrict__ positions,
@@ -58,16 +65,28 @@ __global__ void pack_pair_kernel(float* __restrict__ a, const float* __restrict_
     }
 }
 
+// The same with four elements a thread (16-byte loads of the two streams): widths that are multiples of four.
+template <typename T>
+__global__ void pack_pair_vec_kernel(float* __restrict__ a, const float* __restrict__ b, const float* __restrict__ refill,
+                                     T* __restrict__ out, int d4) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t m = blockIdx.x;
+    float4* ar = (float4*)a + m * d4;
+    const float4* br = (const float4*)b + m * d4;
+    T* o = out + m * 8 * d4;
+    for (int i = threadIdx.x; i < d4; i += blockDim.x) {
+        const float4 x = ar[i], y = br[i];
+        store4(o + 4 * i, x.x, x.y, x.z, x.w);
+        store4(o + 4 * (d4 + i), y.x, y.y, y.z, y.w);
+        if (refill) ar[i] = ((const float4*)refill)[i];
+    }
+}
+
 // y[i, :] = x[r, :] * rsqrt(mean(x[r]^2) + eps) * gain      r = rows ? rows[i] : i
 // (crates/spite-models/src/dense.rs:175-181; the sum runs in float32)
 // One block per row.  The row stays in registers between the sum and the scaling: every thread
 // holds up to VPT groups of four elements, loaded with one 16-byte read each.
-__device__ __forceinline__ void store4(float* p, float a, float b, float c, float d) { *(float4*)p = make_float4(a, b, c, d); }
-__device__ __forceinline__ void store4(__nv_bfloat16* p, float a, float b, float c, float d) {
-    __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
-    *(uint2*)p = make_uint2(*(unsigned*)&lo, *(unsigned*)&hi);
-}
-
 template <typename T, int VPT>
 __global__ void rms_norm_vec_kernel(const float* __restrict__ x, const float* __restrict__ gain,
                                     const int* __restrict__ rows, T* __restrict__ y, int d, float eps) {
@@ -240,7 +259,13 @@ SPITE_API int spite_pack_pair(int out_dtype, float* a, const float* b, const flo
     if (n_rows == 0) return SPITE_OK;
     cudaStream_t st = (cudaStream_t)stream;
     const int threads = d >= 1024 ? 256 : 128;
-    if (out_dtype == SPITE_DT_F32) SPITE_LAUNCH(pack_pair_kernel<float>, n_rows, threads, 0, st, a, b, refill, (float*)out, d);
+    const bool f32 = out_dtype == SPITE_DT_F32;
+    if (d % 4 == 0 && ((((uintptr_t)a | (uintptr_t)b | (uintptr_t)refill | (uintptr_t)out) & 15) == 0)) {
+        if (f32) SPITE_LAUNCH(pack_pair_vec_kernel<float>, n_rows, threads, 0, st, a, b, refill, (float*)out, d / 4);
+        else SPITE_LAUNCH(pack_pair_vec_kernel<__nv_bfloat16>, n_rows, threads, 0, st, a, b, refill, (__nv_bfloat16*)out, d / 4);
+        return spite_launch_status();
+    }
+    if (f32) SPITE_LAUNCH(pack_pair_kernel<float>, n_rows, threads, 0, st, a, b, refill, (float*)out, d);
     else SPITE_LAUNCH(pack_pair_kernel<__nv_bfloat16>, n_rows, threads, 0, st, a, b, refill, (__nv_bfloat16*)out, d);
     return spite_launch_status();
 }
