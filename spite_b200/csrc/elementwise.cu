@@ -47,6 +47,32 @@ __global__ void embed_positions_kernel(const T* __restrict__ table, const int* _
     for (int i = threadIdx.x; i < d; i += blockDim.x) out[i] = to_f32(row[i]) * scale + to_f32(pv[i]);
 }
 
+// The same with four elements a thread: widths that are multiples of four.
+__device__ __forceinline__ float4 load4(const float* p) { return *(const float4*)p; }
+__device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
+    const uint2 v = *(const uint2*)p;
+    const __nv_bfloat162 lo = *(const __nv_bfloat162*)&v.x, hi = *(const __nv_bfloat162*)&v.y;
+    return make_float4(__low2float(lo), __high2float(lo), __low2float(hi), __high2float(hi));
+}
+template <typename T>
+__global__ void embed_positions_vec_kernel(const T* __restrict__ table, const int* __restrict__ tokens,
+                                           const T* __restrict__ pos_table, const int* __restrict__ positions,
+                                           float* __restrict__ h, int d, int vocab, int n_positions, float scale) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int m = blockIdx.x;
+    const int tok = tokens[m], pos = positions[m];
+    float* out = h + (size_t)m * d;
+    const bool ok = tok >= 0 && tok < vocab && pos >= 0 && pos < n_positions;     // the host rejects other steps before the launch
+    const T* row = table + (size_t)(ok ? tok : 0) * d;
+    const T* pv = pos_table + (size_t)(ok ? pos : 0) * d;
+    for (int i = 4 * threadIdx.x; i < d; i += 4 * blockDim.x) {
+        const float4 e = load4(row + i), q = load4(pv + i);
+        *(float4*)(out + i) = ok ? make_float4(e.x * scale + q.x, e.y * scale + q.y, e.z * scale + q.z, e.w * scale + q.w)
+                                 : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+}
+
 // out[m, :] = [a[m, :]; b[m, :]] in the activation type, for two float32 streams of width d; with `refill` every
 // row of a becomes that vector afterwards (a thread overwrites what it has just read itself)
 template <typename T>
@@ -242,6 +268,15 @@ SPITE_API int spite_embed_positions(int dtype, const void* table, const int* tok
     if (n_tokens == 0) return SPITE_OK;
     cudaStream_t st = (cudaStream_t)stream;
     const int threads = d >= 1024 ? 256 : 128;
+    if (d % 4 == 0 && ((((uintptr_t)table | (uintptr_t)pos_table | (uintptr_t)h) & 15) == 0)) {
+        if (dtype == SPITE_DT_F32)
+            SPITE_LAUNCH(embed_positions_vec_kernel<float>, n_tokens, threads, 0, st, (const float*)table, tokens,
+                         (const float*)pos_table, positions, h, d, vocab, n_positions, scale);
+        else
+            SPITE_LAUNCH(embed_positions_vec_kernel<__nv_bfloat16>, n_tokens, threads, 0, st, (const __nv_bfloat16*)table, tokens,
+                         (const __nv_bfloat16*)pos_table, positions, h, d, vocab, n_positions, scale);
+        return spite_launch_status();
+    }
     if (dtype == SPITE_DT_F32)
         SPITE_LAUNCH(embed_positions_kernel<float>, n_tokens, threads, 0, st, (const float*)table, tokens,
                      (const float*)pos_table, positions, h, d, vocab, n_positions, scale);
