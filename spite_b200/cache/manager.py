@@ -70,6 +70,7 @@ class GroupKey:
     window: Window
     num_kv_heads: int
     head_dim: int
+    planes: int = 2
 
 
 class PagePool:

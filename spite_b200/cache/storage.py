@@ -1,6 +1,6 @@
 """Device memory behind the cache manager's page ids and state slots.
 
-One tensor per group, `[caches of the group, 2 (keys, values), pages, kv heads,
+One tensor per group, `[caches of the group, planes (keys, values; or keys alone), pages, kv heads,
 page_size, head_dim]`: for one kv head the `page_size` keys of a page are
 contiguous rows of `head_dim` elements, which is the tile an attention kernel
 loads.  Per-request state of fixed size lives in one tensor per cache that asks
@@ -17,10 +17,12 @@ from .manager import CacheManager, GroupKey, Window
 
 @dataclass(frozen=True)
 class PagedKV:
-    """A mixer's request for paged keys and values."""
+    """A mixer's request for paged keys and values.  `planes` 2: keys and values; 1: keys only (the value of a
+    position is its key row, or a leading part of it)."""
     window: Window
     num_kv_heads: int
     head_dim: int
+    planes: int = 2
 
 
 @dataclass(frozen=True)
@@ -36,7 +38,7 @@ class LayerCache:
     def __init__(self, group: int | None, kv: torch.Tensor | None, state: torch.Tensor | None,
                  page_size: int, write: bool):
         self.group = group          # index of the block table to use
-        self.kv = kv                # [2, pages, kv heads, page_size, head_dim] or None
+        self.kv = kv                # [planes, pages, kv heads, page_size, head_dim] or None
         self.state = state          # [slots, *shape] or None
         self.page_size = page_size
         self.write = write          # this run appends its keys and values
@@ -57,7 +59,7 @@ class CacheStorage:
             kv, _ = cache_specs[cid]
             if kv is None:
                 continue
-            key = GroupKey(kv.window, kv.num_kv_heads, kv.head_dim)
+            key = GroupKey(kv.window, kv.num_kv_heads, kv.head_dim, kv.planes)
             if key not in keys:
                 keys.append(key)
                 counts.append(0)
@@ -68,7 +70,7 @@ class CacheStorage:
         self.group_keys = keys
         self.manager = CacheManager(keys, page_size, pages if keys else 1, n_slots) if keys else \
             CacheManager([], page_size, [], n_slots)
-        self.kv = [torch.zeros((counts[g], 2, pages, k.num_kv_heads, page_size, k.head_dim),
+        self.kv = [torch.zeros((counts[g], k.planes, pages, k.num_kv_heads, page_size, k.head_dim),
                                dtype=dtype, device=self.device) for g, k in enumerate(keys)]
         self.state = {}
         for cid, (_, st) in cache_specs.items():

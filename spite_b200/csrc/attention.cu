@@ -1,5 +1,5 @@
 // Attention over the paged cache, general kernels (any head size that is a
-// multiple of 2 up to 256, any number of heads and groups, both element types).
+// multiple of 2 up to 256 (the attention kernel: up to 640), any number of heads and groups, both element types).
 //
 //  * qk_prepare: position encoding of q and k (neighbouring elements or the two halves of
 //    the rotating part pair up), per-head RMS norm after or before it with or without gains,
@@ -37,6 +37,10 @@ __global__ void __launch_bounds__(256) qk_prepare_kernel(const QkPrepareParams p
     const int heads_total = nq + 2 * nkv;
     const int head_end = min(heads_total, (int)(blockIdx.y + 1) * heads_per_block);
     const int pos = b.positions[t];
+    if (p.gates_out && blockIdx.y == 0)                      // the gate columns behind the heads
+        for (int h = threadIdx.x; h < nq; h += blockDim.x)
+            p.gates_out[(size_t)t * nq + h] =
+                1.0f / (1.0f + expf(-to_f32(((const T*)p.qkv)[(size_t)t * p.qkv_stride + (size_t)heads_total * hd + h])));
     int page = -1;
     if (p.write_cache) {
         page = b.block_table[(size_t)b.seg_of_token[t] * b.table_width + pos / c.page_size];
@@ -56,7 +60,10 @@ __global__ void __launch_bounds__(256) qk_prepare_kernel(const QkPrepareParams p
     // cos and sin of a position's angles are the same for every head: the block computes each once (the exact
     // sincosf of an angle of thousands of radians is the most expensive thing here) and its warps read them
     __shared__ float cs_s[128], sn_s[128];
-    for (int i = threadIdx.x; 2 * i < rot; i += blockDim.x) sincosf((float)pos * p.inv_freq[i], &sn_s[i], &cs_s[i]);
+    for (int i = threadIdx.x; 2 * i < rot; i += blockDim.x) {
+        sincosf((float)pos * p.inv_freq[i], &sn_s[i], &cs_s[i]);
+        sn_s[i] *= p.rot_amplitude; cs_s[i] *= p.rot_amplitude;
+    }
     __syncthreads();
     float cs[MAXP], sn[MAXP];
     int e0[MAXP], e1[MAXP];                                  // (neighbours: known at compile time, no registers)
@@ -76,7 +83,7 @@ __global__ void __launch_bounds__(256) qk_prepare_kernel(const QkPrepareParams p
     const bool norm = p.qk_norm_eps > 0.f;
     const bool norm_first = norm && p.norm_before_rotation;
     for (int head = blockIdx.y * heads_per_block + warp; head < head_end; head += n_warps) {
-        const T* in = (const T*)p.qkv + (size_t)t * heads_total * hd + (size_t)head * hd;
+        const T* in = (const T*)p.qkv + (size_t)t * p.qkv_stride + (size_t)head * hd;
         const bool is_q = head < nq, is_v = head >= nq + nkv;
         T* dst;
         if (is_q) {
@@ -88,9 +95,15 @@ __global__ void __launch_bounds__(256) qk_prepare_kernel(const QkPrepareParams p
                   (((size_t)page * nkv + kvh) * c.page_size + pos % c.page_size) * hd;
         }
         if (is_v) {
+            const T* other = p.v_other ? (const T*)p.v_other + (size_t)t * p.v_other_stride +
+                                         (size_t)(head - nq - nkv) * p.v_other_head : nullptr;
             for (int i = lane; 2 * i < hd; i += 32) {
                 float a, bb;
                 load_pair(in + 2 * i, a, bb);
+                if (other) {                                 // blended with the other layer's value of this token
+                    if (2 * i < p.v_mix_dim) a = (1.0f - p.v_mix) * a + p.v_mix * to_f32(other[2 * i]);
+                    if (2 * i + 1 < p.v_mix_dim) bb = (1.0f - p.v_mix) * bb + p.v_mix * to_f32(other[2 * i + 1]);
+                }
                 store_pair(dst + 2 * i, a, bb);
             }
             continue;
@@ -148,10 +161,10 @@ __global__ void __launch_bounds__(256) qk_prepare_kernel(const QkPrepareParams p
 // grid (tokens, ceil(nq / 4)), block 128: one warp per (token, query head).
 // crates/spite-compute/src/flash_attn.rs:111-156 with the maximum and the sum kept
 // as running values over tiles of 32 keys.
-template <typename T>
+template <typename T, int MAXD>
 __global__ void __launch_bounds__(128) paged_attention_kernel(const AttentionParams p, const StepTokens b,
                                                               const PagedCache c) {
-    __shared__ float q_s[4][256];
+    __shared__ float q_s[4][32 * MAXD];                      // head_dim <= 32 * MAXD
     pdl_wait();
     pdl_launch_dependents();
 
@@ -172,11 +185,11 @@ __global__ void __launch_bounds__(128) paged_attention_kernel(const AttentionPar
 
     const T* kbase = (const T*)c.kv;
     const T* vbase = (const T*)c.kv + c.v_offset;
-    constexpr int MAXD = 8;                                  // head_dim <= 256
     float acc[MAXD];
 #pragma unroll
     for (int r = 0; r < MAXD; ++r) acc[r] = 0.f;
     float m = -INFINITY, l = 0.f;
+    const float slope = slope_of(p, h);
 
     for (int j0 = lo; j0 <= pos; j0 += 32) {
         const int j = j0 + lane;
@@ -188,7 +201,7 @@ __global__ void __launch_bounds__(128) paged_attention_kernel(const AttentionPar
             const T* k = kbase + row;
             float dot = 0.f;
             for (int d = 0; d < hd; ++d) dot = fmaf(q_s[warp][d], to_f32(k[d]), dot);
-            s = dot * p.softmax_scale;
+            s = dot * p.softmax_scale - slope * (float)(pos - j);
         }
         const float m_new = fmaxf(m, warp_max(s));
         const float corr = expf(m - m_new);                  // 0 on the first tile (m = -inf)
@@ -209,14 +222,15 @@ __global__ void __launch_bounds__(128) paged_attention_kernel(const AttentionPar
         }
         m = m_new;
     }
-    if (p.has_sink) {                                        // one more key, of score sink_logit and value zero
-        const float m_new = fmaxf(m, p.sink_logit);
+    if (p.has_sink) {                                        // one more key, of the sink's score and value zero
+        const float sink = sink_of(p, h);
+        const float m_new = fmaxf(m, sink);
         const float corr = expf(m - m_new);
-        l = l * corr + expf(p.sink_logit - m_new);
+        l = l * corr + expf(sink - m_new);
 #pragma unroll
         for (int r = 0; r < MAXD; ++r) acc[r] *= corr;
     }
-    const float inv = 1.0f / fmaxf(l, 1e-30f);
+    const float inv = gate_of(p, t, h) / fmaxf(l, 1e-30f);
     T* out = (T*)p.out + ((size_t)t * nq + h) * hd;
 #pragma unroll
     for (int r = 0; r < MAXD; ++r) {
@@ -225,12 +239,12 @@ __global__ void __launch_bounds__(128) paged_attention_kernel(const AttentionPar
     }
 }
 
-int check_common(const StepTokens* b, const PagedCache* c, int num_heads) {
+int check_common(const StepTokens* b, const PagedCache* c, int num_heads, int max_head_dim = 256) {
     if (!b || !c || !b->positions || !b->seg_of_token || !b->block_table || !c->kv) return SPITE_BAD_ARG;
     if (b->n_tokens < 0 || b->table_width < 1 || c->n_pages < 1 || c->page_size < 1) return SPITE_BAD_ARG;
     if (num_heads < 1 || c->num_kv_heads < 1 || num_heads % c->num_kv_heads) return SPITE_BAD_ARG;
     if (c->head_dim < 2 || c->head_dim % 2) return SPITE_BAD_ARG;
-    if (c->head_dim > 256) return SPITE_UNSUPPORTED;
+    if (c->head_dim > max_head_dim) return SPITE_UNSUPPORTED;
     return SPITE_OK;
 }
 
@@ -246,6 +260,9 @@ SPITE_API int spite_qk_prepare(int dtype, const QkPrepareParams* p, const StepTo
     if (p->inv_freq && (p->rotary_dim < 2 || p->rotary_dim % 2 || p->rotary_dim > c->head_dim)) return SPITE_BAD_ARG;
     if (p->pairing == SPITE_PAIR_HALVES && p->inv_freq && p->rotary_dim % 4) return SPITE_UNSUPPORTED;  // pairs beyond the rotating part start at an even pair index
     const int heads = p->num_heads + 2 * c->num_kv_heads;
+    if (p->qkv_stride < (long long)heads * c->head_dim || (p->qkv_stride & 1)) return SPITE_BAD_ARG;
+    if (p->gates_out && p->qkv_stride < (long long)heads * c->head_dim + p->num_heads) return SPITE_BAD_ARG;
+    if (p->v_other && (p->v_mix_dim < 0 || p->v_mix_dim > c->head_dim || p->v_other_head < p->v_mix_dim)) return SPITE_BAD_ARG;
     // few tokens: four heads a block, so that the step still fills the device; many: a block per token
     const bool many = b->n_tokens >= 1024;
     const int heads_per_block = many ? 16 : 4;
@@ -269,7 +286,7 @@ SPITE_API int spite_qk_prepare(int dtype, const QkPrepareParams* p, const StepTo
 SPITE_API int spite_paged_attention(int dtype, const AttentionParams* p, const StepTokens* b,
                                     const PagedCache* c, void* stream) {
     if (!p || !p->q || !p->out) return SPITE_BAD_ARG;
-    const int chk = check_common(b, c, p->num_heads);
+    const int chk = check_common(b, c, p->num_heads, 640);
     if (chk != SPITE_OK) return chk;
     if (p->window_kind < 0 || p->window_kind > 2) return SPITE_BAD_ARG;
     if (p->window_kind != SPITE_WINDOW_FULL && p->window_size < 1) return SPITE_BAD_ARG;
@@ -277,8 +294,13 @@ SPITE_API int spite_paged_attention(int dtype, const AttentionParams* p, const S
     dim3 grid(b->n_tokens, (p->num_heads + 3) / 4);
     if (grid.y > 65535) return SPITE_UNSUPPORTED;
     cudaStream_t st = (cudaStream_t)stream;
-    if (dtype == SPITE_DT_F32) SPITE_LAUNCH(paged_attention_kernel<float>, grid, 128, 0, st, *p, *b, *c);
-    else if (dtype == SPITE_DT_BF16) SPITE_LAUNCH(paged_attention_kernel<__nv_bfloat16>, grid, 128, 0, st, *p, *b, *c);
-    else return SPITE_BAD_ARG;
+    const bool wide = c->head_dim > 256;                     // rows of up to 640 elements (latent caches)
+    if (dtype == SPITE_DT_F32) {
+        if (wide) SPITE_LAUNCH((paged_attention_kernel<float, 20>), grid, 128, 0, st, *p, *b, *c);
+        else SPITE_LAUNCH((paged_attention_kernel<float, 8>), grid, 128, 0, st, *p, *b, *c);
+    } else if (dtype == SPITE_DT_BF16) {
+        if (wide) SPITE_LAUNCH((paged_attention_kernel<__nv_bfloat16, 20>), grid, 128, 0, st, *p, *b, *c);
+        else SPITE_LAUNCH((paged_attention_kernel<__nv_bfloat16, 8>), grid, 128, 0, st, *p, *b, *c);
+    } else return SPITE_BAD_ARG;
     return spite_launch_status();
 }

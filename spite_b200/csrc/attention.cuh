@@ -19,6 +19,7 @@ struct StepTokens {
 
 // One cache: keys at kv, values at kv + v_offset (elements); a page holds, for every
 // kv head, page_size rows of head_dim elements: [pages][kv heads][page_size][head_dim].
+// v_offset 0: the cache has keys only and a position's value is its key row.
 struct PagedCache {
     void* kv;
     long long v_offset;
@@ -45,6 +46,17 @@ struct QkPrepareParams {
     float temperature_scale;
     int num_heads;
     int write_cache;            // append k and v to the cache
+    long long qkv_stride;       // elements between two tokens' rows of qkv (>= (nq + 2 nkv) * head_dim)
+    float rot_amplitude;        // cos and sin of the rotation are multiplied by this (1: a pure rotation)
+    // value blending: element i < v_mix_dim of kv head g's value becomes (1 - v_mix) v + v_mix * v_other[t * v_other_stride +
+    // g * v_other_head + i] before it is cached (v_other null: no blending)
+    const void* v_other;
+    long long v_other_stride;
+    int v_other_head;
+    int v_mix_dim;
+    float v_mix;
+    // gates_out[t * nq + h] = sigmoid(qkv[t * qkv_stride + (nq + 2 nkv) * head_dim + h]) (null: no gate columns)
+    float* gates_out;
 };
 
 struct AttentionParams {
@@ -56,16 +68,33 @@ struct AttentionParams {
     float softmax_scale;
     int has_sink;               // the softmax's denominator also holds exp(sink_logit): a key every query sees
     float sink_logit;           // and that adds nothing to the output (a score of 0 puts exp(0) = 1 into the sum)
+    const float* head_sinks;    // [num_heads] or null: with has_sink, head h's sink has the score head_sinks[h] instead
+    const float* head_slopes;   // [num_heads] or null: head_slopes[h] * (query position - key position) is taken off a score
+    const float* head_gates;    // [tokens, num_heads] or null: head h's output of token t is multiplied by head_gates[t * nq + h]
 };
+
+// The score of head `head`'s sink (only meaningful with has_sink).
+__device__ __forceinline__ float sink_of(const AttentionParams& p, int head) {
+    return p.head_sinks ? p.head_sinks[head] : p.sink_logit;
+}
+// What is taken off the score of a key `distance` positions before the query.
+__device__ __forceinline__ float slope_of(const AttentionParams& p, int head) {
+    return p.head_slopes ? p.head_slopes[head] : 0.f;
+}
+// The factor on a finished output row.
+__device__ __forceinline__ float gate_of(const AttentionParams& p, int token, int head) {
+    return p.head_gates ? p.head_gates[(size_t)token * p.num_heads + head] : 1.f;
+}
 
 // The sink folded into a finished softmax state: `m` and `l` are the maximum and the sum of exp(s - m) over the
 // real keys (natural-log units).  Afterwards l is the whole denominator relative to max(m, sink); the return
 // value is the factor by which the accumulated values shrink to the same reference.
-__device__ __forceinline__ float fold_sink(const AttentionParams& p, float m, float& l) {
+__device__ __forceinline__ float fold_sink(const AttentionParams& p, int head, float m, float& l) {
     if (!p.has_sink) return 1.f;
-    const float m2 = fmaxf(m, p.sink_logit);
+    const float sink = sink_of(p, head);
+    const float m2 = fmaxf(m, sink);
     const float f = (m == -INFINITY) ? 0.f : expf(m - m2);
-    l = l * f + expf(p.sink_logit - m2);
+    l = l * f + expf(sink - m2);
     return f;
 }
 

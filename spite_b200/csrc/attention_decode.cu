@@ -172,6 +172,7 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const __grid_const
         // ---- consumers: warp w takes keys 16 w .. 16 w + 15 of every tile
         const int g = lane >> 2, cc = lane & 3;
         int row_pos[2], row_lo[2];
+        float row_slope[2];                                  // what a key costs per position of distance (0: no bias)
         bool row_ok[2];
         unsigned qa[NK][4];
 #pragma unroll
@@ -181,6 +182,7 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const __grid_const
             const int tok = t0 + (row_ok[h] ? r / G : 0);
             const int head = kvh * G + (row_ok[h] ? r % G : 0);
             row_pos[h] = b.positions[tok];
+            row_slope[h] = slope_of(p, head);
             row_lo[h] = window_lowest(p.window_kind, p.window_size, row_pos[h]);
             const __nv_bfloat16* qrow = (const __nv_bfloat16*)p.q + ((size_t)tok * nq + head) * HD;
 #pragma unroll
@@ -230,7 +232,7 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const __grid_const
                         for (int e = 0; e < 2; ++e) {
                             const int j = j0 + 8 * n + 2 * cc + e;
                             const bool vis = row_ok[h] && j >= row_lo[h] && j <= row_pos[h];
-                            const float v = vis ? sc[n][2 * h + e] * p.softmax_scale : -INFINITY;
+                            const float v = vis ? sc[n][2 * h + e] * p.softmax_scale - row_slope[h] * (float)(row_pos[h] - j) : -INFINITY;
                             sc[n][2 * h + e] = v;
                             mx = fmaxf(mx, v);
                         }
@@ -316,7 +318,7 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const __grid_const
         }
         if (x.n_splits == 1) {
             const int tok = t0 + r / G, head = kvh * G + r % G;
-            acc *= fold_sink(p, m, l);
+            acc *= fold_sink(p, head, m, l) * gate_of(p, tok, head);
             ((__nv_bfloat16*)p.out)[((size_t)tok * nq + head) * HD + d] = __float2bfloat16_rn(acc / fmaxf(l, 1e-30f));
         } else {
             __stcg(part + r * ROW + d, acc);
@@ -382,8 +384,9 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const __grid_const
             }
             l += warp_sum(ls);
         }
-        const float shrink = fold_sink(p, m, l);             // the sink joins once, after the splits have met
-        if (lane == 0) inv_s[r] = shrink / fmaxf(l, 1e-30f);
+        const int tok = t0 + r / G, head = kvh * G + r % G;
+        const float shrink = fold_sink(p, head, m, l);       // the sink joins once, after the splits have met
+        if (lane == 0) inv_s[r] = shrink * gate_of(p, tok, head) / fmaxf(l, 1e-30f);
     }
     consumer_sync();
     for (int e = threadIdx.x; e < n_items; e += CONSUMERS * 32) {

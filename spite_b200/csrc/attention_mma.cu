@@ -84,6 +84,7 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const AttentionPar
 
     // the two rows of this lane: g and g + 8
     int row_pos[2], row_lo[2];
+    float row_slope[2];                                     // what a key costs per position of distance (0: no bias)
     bool row_ok[2];
     const __nv_bfloat16* qrow[2];
 #pragma unroll
@@ -93,6 +94,7 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const AttentionPar
         const int tok = t0 + (row_ok[h] ? r / G : 0);
         const int head = kvh * G + (row_ok[h] ? r % G : 0);
         row_pos[h] = b.positions[tok];
+        row_slope[h] = slope_of(p, head);
         row_lo[h] = window_lowest(p.window_kind, p.window_size, row_pos[h]);
         qrow[h] = (const __nv_bfloat16*)p.q + ((size_t)tok * nq + head) * HD;
     }
@@ -188,7 +190,7 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const AttentionPar
                 for (int e = 0; e < 2; ++e) {
                     const int j = j0 + 8 * n + 2 * cc + e;
                     const bool ok = row_ok[h] && j >= row_lo[h] && j <= row_pos[h];
-                    const float v = ok ? s[n][2 * h + e] * p.softmax_scale : -INFINITY;
+                    const float v = ok ? s[n][2 * h + e] * p.softmax_scale - row_slope[h] * (float)(row_pos[h] - j) : -INFINITY;
                     s[n][2 * h + e] = v;
                     mx = fmaxf(mx, v);
                 }
@@ -265,7 +267,7 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const AttentionPar
         }
         const int tok = t0 + r / G, head = kvh * G + r % G;
         if (x.n_splits == 1) {
-            acc *= fold_sink(p, m, l);
+            acc *= fold_sink(p, head, m, l) * gate_of(p, tok, head);
             ((__nv_bfloat16*)p.out)[((size_t)tok * nq + head) * HD + d] = __float2bfloat16_rn(acc / fmaxf(l, 1e-30f));
         } else {
             // partial results are indexed by the block's place among this kernel's blocks, not by the
@@ -320,8 +322,8 @@ __global__ void __launch_bounds__(MERGE_THREADS) attn_merge_kernel(const float* 
     const float w = ms > -INFINITY ? expf(ms - m) : 0.f;
     w_s[tid] = w;
     float l = block_sum(ls * w, scratch);                   // syncs: w_s is visible afterwards
-    const float shrink = fold_sink(p, m, l);                // the sink joins once, after the splits have met
-    const float inv = shrink / fmaxf(l, 1e-30f);
+    const float shrink = fold_sink(p, head, m, l);          // the sink joins once, after the splits have met
+    const float inv = shrink * gate_of(p, tok, head) / fmaxf(l, 1e-30f);
     const float* o = o_part + row * n_splits * hd;
     __nv_bfloat16* dst = out + ((size_t)tok * num_heads + head) * hd;
     for (int d = tid; d < hd; d += MERGE_THREADS) {

@@ -79,6 +79,7 @@ __global__ void __launch_bounds__(WARPS * 32) attn_rows_kernel(const AttentionPa
 
     // the two rows of this lane: 16 * warp + g and + 8
     int row_pos[2], row_lo[2];
+    float row_slope[2];                                     // what a key costs per position of distance (0: no bias)
     bool row_ok[2];
     const __nv_bfloat16* qrow[2];
 #pragma unroll
@@ -88,6 +89,7 @@ __global__ void __launch_bounds__(WARPS * 32) attn_rows_kernel(const AttentionPa
         const int tok = t0 + (row_ok[h] ? r / G : 0);
         const int head = kvh * G + (row_ok[h] ? r % G : 0);
         row_pos[h] = b.positions[tok];
+        row_slope[h] = slope_of(p, head);
         row_lo[h] = window_lowest(p.window_kind, p.window_size, row_pos[h]);
         qrow[h] = (const __nv_bfloat16*)p.q + ((size_t)tok * nq + head) * HD;
     }
@@ -185,7 +187,7 @@ __global__ void __launch_bounds__(WARPS * 32) attn_rows_kernel(const AttentionPa
                     for (int e = 0; e < 2; ++e) {
                         const int j = j0 + 8 * n + 2 * cc + e;
                         const bool ok = row_ok[h] && j >= row_lo[h] && j <= row_pos[h];
-                        const float v = ok ? s[n][2 * h + e] * p.softmax_scale : -INFINITY;
+                        const float v = ok ? s[n][2 * h + e] * p.softmax_scale - row_slope[h] * (float)(row_pos[h] - j) : -INFINITY;
                         s[n][2 * h + e] = v;
                         mx = fmaxf(mx, v);
                     }
@@ -237,8 +239,8 @@ __global__ void __launch_bounds__(WARPS * 32) attn_rows_kernel(const AttentionPa
         const int r = 16 * warp + g + 8 * h;
         const int tok = t0 + r / G, head = kvh * G + r % G;
         float l = l_run[h];
-        const float shrink = fold_sink(p, m_run[h], l);
-        const float inv = shrink / fmaxf(l, 1e-30f);
+        const float shrink = fold_sink(p, head, m_run[h], l);
+        const float inv = shrink * gate_of(p, tok, head) / fmaxf(l, 1e-30f);
         __nv_bfloat16* dst = (__nv_bfloat16*)p.out + ((size_t)tok * nq + head) * HD + 2 * cc;
 #pragma unroll
         for (int n = 0; n < 2 * NK; ++n)

@@ -302,6 +302,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 const int pos = row_ok ? b.positions[tok] : -1;   // a row without a token sees no key
                 const int lo = window_lowest(p.window_kind, p.window_size, max(pos, 0));
                 const float scale = p.softmax_scale * LOG2E;
+                // a bias that grows with the distance to the key, in units of the raw scores (they are multiplied by
+                // the scale afterwards): its rounding error is relative to the bias itself
+                const bool biased = p.head_slopes != nullptr;
+                const float bias_raw = slope_of(p, head) / p.softmax_scale;
                 const unsigned lane_base = tmem_g + ((unsigned)(quarter * 32) << 16);
                 float m_ref = -INFINITY, l = 0.f;
                 bool ok = true;
@@ -316,6 +320,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                     const bool open = j0 >= lo_last && j0 + BN - 1 <= p_first;   // every key visible to every row with a token
                     // maximum of the raw scores (the scale is positive); four running values shorten the chain
                     float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+                    if (biased) {
+#pragma unroll
+                        for (int e = 0; e < BN; ++e) s[e] = fmaf(bias_raw, (float)(j0 + e - pos), s[e]);
+                    }
                     if (!open) {                                   // a tile on a window's edge or on the diagonal
 #pragma unroll
                         for (int e = 0; e < BN; ++e) {
@@ -383,11 +391,11 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                     fence_after();
                     float shrink = 1.f;
                     if (p.has_sink) {                              // the sink's score in this kernel's units (powers of two)
-                        const float sink2 = p.sink_logit * LOG2E, m2 = fmaxf(m_ref, sink2);
+                        const float sink2 = sink_of(p, head) * LOG2E, m2 = fmaxf(m_ref, sink2);
                         shrink = (m_ref == -INFINITY) ? 0.f : exp2f(m_ref - m2);
                         l = l * shrink + exp2f(sink2 - m2);
                     }
-                    const float inv = shrink / fmaxf(l, 1e-30f);
+                    const float inv = shrink * gate_of(p, tok, head) / fmaxf(l, 1e-30f);
                     __nv_bfloat16* dst = (__nv_bfloat16*)p.out + ((size_t)tok * nq + head) * HD;
 #pragma unroll 1
                     for (int c0 = 0; c0 < HD; c0 += 32) {

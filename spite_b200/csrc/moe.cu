@@ -3,12 +3,15 @@
 // logits: l = Wr x in float32 (crates/spite-models/src/moe.rs:65-66).
 // select: the k largest raw logits are chosen, equal logits preferring the lower expert
 //   id (moe.rs:110-116, a stable descending sort); the weight is sigmoid(logit)
-//   (moe.rs:120).  No softmax, no renormalisation.
+//   (moe.rs:120).  No softmax, no renormalisation.  A second scoring rule, SCORE_SOFTMAX_RENORM: the weight
+//   of a choice is its share of the softmax over all experts divided by the sum of the chosen shares
+//   (+ 1e-20), all float32; the order of the experts is the same (the softmax is monotonic).
 //   Choices are stored slot-major: expert_ids[slot][token], weights[slot][token].
 // sort: for every choice slot a stable counting sort of the tokens by expert:
 //   offsets[slot][e] .. offsets[slot][e+1] are the places of expert e's tokens in
-//   sorted_rows[slot][:], in ascending token order.  No host round trip: the grouped
-//   products read these arrays on the device.
+//   sorted_rows[slot][:], in ascending token order; sorted_weights[slot][i], if asked for, is the
+//   weight of the token at place i (for a product that scales its rows in the sorted order).
+//   No host round trip: the grouped products read these arrays on the device.
 //
 // Two kernels.  The first computes the logits (8 tokens x 2 experts at a time, the block's 8
 // warps splitting the width), one pair of experts a block, so that a few tokens still spread over
@@ -22,6 +25,7 @@ constexpr int MAX_EXPERTS = 1024;
 constexpr int TB = 8;                  // tokens per block of the logits kernel
 constexpr int EB = 2;                  // experts per block
 constexpr int WARPS = 8;
+constexpr int SCORE_SIGMOID = 0, SCORE_SOFTMAX_RENORM = 1;
 
 __device__ __forceinline__ void load4(const float* p, float (&v)[4]) {
     const float4 t = *(const float4*)p;
@@ -116,7 +120,8 @@ __global__ void __launch_bounds__(1024) select_and_sort_kernel(const float* __re
                                                                int n_experts, int top_k,
                                                                int* __restrict__ expert_ids, float* __restrict__ weights,
                                                                int* __restrict__ offsets,
-                                                               int* __restrict__ sorted_rows) {
+                                                               int* __restrict__ sorted_rows, int scoring,
+                                                               float* __restrict__ sorted_weights) {
     __shared__ int counts[MAX_EXPERTS + 1];
     pdl_wait();
     pdl_launch_dependents();
@@ -130,9 +135,11 @@ __global__ void __launch_bounds__(1024) select_and_sort_kernel(const float* __re
         const float* l = logits + (size_t)t * n_experts;
         float prev_v = INFINITY;
         int prev_e = -1;
-        float best_v = 0.f;
-        int best_e = 0;
-        for (int s = 0; s <= slot; ++s) {
+        float best_v = 0.f, mine_v = 0.f;
+        int best_e = 0, mine_e = 0;
+        float chosen_max = 0.f, chosen_sum = 0.f;            // of exp(logit - largest logit) over the chosen experts
+        const int picks = scoring == SCORE_SOFTMAX_RENORM ? top_k : slot + 1;
+        for (int s = 0; s < picks; ++s) {
             best_v = -INFINITY;
             best_e = -1;
             for (int e = 0; e < n_experts; ++e) {
@@ -143,10 +150,22 @@ __global__ void __launch_bounds__(1024) select_and_sort_kernel(const float* __re
             if (best_e < 0) { best_e = 0; best_v = l[0]; }    // logits that do not compare (NaN): still a valid id
             prev_v = best_v;
             prev_e = best_e;
+            if (s == 0) chosen_max = best_v;                 // the largest logit of all
+            chosen_sum += expf(best_v - chosen_max);
+            if (s == slot) { mine_v = best_v; mine_e = best_e; }
         }
-        ids[t] = best_e;
-        weights[(size_t)slot * n_tokens + t] = 1.0f / (1.0f + expf(-best_v));
-        atomicAdd(&counts[best_e + 1], 1);
+        ids[t] = mine_e;
+        float w;
+        if (scoring == SCORE_SOFTMAX_RENORM) {
+            // share_e = exp(l_e - max) / Z with Z over all experts; w = share / (sum of chosen shares + 1e-20)
+            float z = 0.f;
+            for (int e = 0; e < n_experts; ++e) z += expf(l[e] - chosen_max);
+            w = (expf(mine_v - chosen_max) / z) / (chosen_sum / z + 1e-20f);
+        } else {
+            w = 1.0f / (1.0f + expf(-mine_v));
+        }
+        weights[(size_t)slot * n_tokens + t] = w;
+        atomicAdd(&counts[mine_e + 1], 1);
     }
     __syncthreads();
     if (threadIdx.x == 0)
@@ -162,7 +181,11 @@ __global__ void __launch_bounds__(1024) select_and_sort_kernel(const float* __re
             const int t = t0 + lane;
             const bool mine = t < n_tokens && ids[t] == e;
             const unsigned mask = __ballot_sync(0xffffffffu, mine);
-            if (mine) rows[base + __popc(mask & ((1u << lane) - 1u))] = t;
+            if (mine) {
+                const int at = base + __popc(mask & ((1u << lane) - 1u));
+                rows[at] = t;
+                if (sorted_weights) sorted_weights[(size_t)slot * n_tokens + at] = weights[(size_t)slot * n_tokens + t];
+            }
             base += __popc(mask);
         }
     }
@@ -173,8 +196,10 @@ __global__ void __launch_bounds__(1024) select_and_sort_kernel(const float* __re
 // `logits` [tokens, experts] float32 is always written (the caller owns it).
 SPITE_API int spite_moe_route(int dtype, const void* x, const float* w_router, int n_tokens, int d,
                               int n_experts, int top_k, int* expert_ids, float* weights,
-                              float* logits, int* offsets, int* sorted_rows, void* stream) {
+                              float* logits, int* offsets, int* sorted_rows, int scoring, float* sorted_weights,
+                              void* stream) {
     if (!x || !w_router || !expert_ids || !weights || !logits || !offsets || !sorted_rows) return SPITE_BAD_ARG;
+    if (scoring != SCORE_SIGMOID && scoring != SCORE_SOFTMAX_RENORM) return SPITE_BAD_ARG;
     if (n_tokens < 0 || d <= 0 || n_experts < 1 || top_k < 1 || top_k > n_experts) return SPITE_BAD_ARG;
     if (n_experts > MAX_EXPERTS) return SPITE_UNSUPPORTED;
     cudaStream_t st = (cudaStream_t)stream;
@@ -195,6 +220,6 @@ SPITE_API int spite_moe_route(int dtype, const void* x, const float* w_router, i
         if (cudaGetLastError() != cudaSuccess) return SPITE_LAUNCH_FAILED;
     }
     SPITE_LAUNCH(select_and_sort_kernel, top_k, 1024, 0, st, (const float*)logits, n_tokens, n_experts, top_k,
-                 expert_ids, weights, offsets, sorted_rows);
+                 expert_ids, weights, offsets, sorted_rows, scoring, sorted_weights);
     return spite_launch_status();
 }

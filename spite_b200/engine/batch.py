@@ -36,6 +36,8 @@ class StepBatch:
     max_seg_len: int = 0
     context_bucket: int | None = None   # steps replayed from a CUDA graph: launch shapes are chosen for
                                         # this context length instead of the step's own
+    shared: dict = field(default_factory=dict)   # what one layer of the step leaves for a later one (emptied when a
+                                                 # forward pass starts)
 
 
 def build_step_batch(segments, tokens_per_segment, wants, tables_per_group, device, pin=True) -> StepBatch:

@@ -49,10 +49,15 @@ class Engine:
         self.model = model
         self.page_size = page_size
         self.n_pages = max(1, -(-int(cache_tokens) // page_size))
-        self.max_positions = int(max_positions or model.plan.max_positions)
         self.storage = CacheStorage(model.cache_specs(), page_size, self.n_pages, max_requests,
                                     model.dtype, model.device)
         self.cache = self.storage.manager
+        self.max_positions = int(max_positions or model.plan.max_positions)
+        # pages a block table of a captured decode step has room for: a request's length is bounded by the position
+        # limit and, where a group of layers keeps every key, by what the pool holds
+        self._table_width = -(-self.max_positions // page_size)
+        if any(key.window.kind == "full" for key in self.storage.group_keys):
+            self._table_width = min(self._table_width, self.n_pages)
         self.steps_run = 0
         self.tokens_run = 0
         # Decode steps (one token per request) are launch-bound: their kernels are captured in
@@ -211,8 +216,7 @@ class Engine:
                 # a replay of the graph that goes may still be running, and its buffers are about to be freed
                 torch.cuda.current_stream(self.model.device).synchronize()
                 self._graphs.popitem(last=False)
-            width = -(-self.max_positions // self.page_size)
-            st = _GraphState(StaticDecodeBatch(S, [width] * self.storage.n_groups, self.model.device, bucket))
+            st = _GraphState(StaticDecodeBatch(S, [self._table_width] * self.storage.n_groups, self.model.device, bucket))
             self._graphs[key] = st
         else:
             self._graphs.move_to_end(key)

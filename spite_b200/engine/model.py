@@ -190,6 +190,7 @@ class Model:
         float32 logits [wanted rows, vocab]."""
         k = self.kernels
         p = self.plan
+        batch.shared.clear()
         h = torch.empty((batch.n_tokens, p.hidden_size), dtype=torch.float32, device=self.device)
         if self.position_table is None:
             k.embed(self.embed_table, batch.token_ids, h, scale=p.embedding_scale)

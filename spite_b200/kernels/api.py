@@ -34,6 +34,7 @@ class Routing:
     offsets: torch.Tensor        # [k, E + 1] int32: places of each expert's tokens in sorted_rows
     sorted_rows: torch.Tensor    # [k, M] int32: token indices ordered by expert, ascending within one
     logits: Optional[torch.Tensor] = None   # [M, E] float32 if asked for
+    sorted_weights: Optional[torch.Tensor] = None   # [k, M] float32: weights[slot][sorted_rows[slot][i]] at place i
 
 
 class KernelSet:
@@ -90,8 +91,15 @@ class KernelSet:
         range of `offsets` holds i; w_up [E, F, K]; row_scale [M] by token; "relu2": act(y) = relu(y)^2."""
         raise NotImplementedError
 
-    def grouped_linear_accumulate(self, a, w_down, sorted_rows, offsets, h):
-        """h[sorted_rows[i], :] (float32) += a[i, :] @ w_down[expert of i]^T; w_down [E, d, F]."""
+    def grouped_linear_accumulate(self, a, w_down, sorted_rows, offsets, h, *, row_scale=None):
+        """h[sorted_rows[i], :] (float32) += s_i * (a[i, :] @ w_down[expert of i]^T); w_down [E, d, F];
+        `row_scale` [M] float32 by place i in the sorted order (s_i = 1 without it)."""
+        raise NotImplementedError
+
+    def grouped_linear_rows(self, a, w, rows, offsets, out):
+        """out[rows[i], :N] (T) = a[rows[i], :K] @ w[g]^T for every place i of group g's range of `offsets`;
+        a [R, lda >= K], w [G, N, K], out [R, ldc >= N].  Rows of `a` and `out` that no place names, and columns
+        beyond K and N, are neither read nor written (a product per head: the rows are (token, head) pairs)."""
         raise NotImplementedError
 
     # ---- cache
@@ -102,25 +110,54 @@ class KernelSet:
         raise NotImplementedError
 
     # ---- attention
-    def qk_prepare(self, qkv, q_out, batch, cache, *, num_heads, rotation, qk_norm, temperature):
+    def qk_prepare(self, qkv, q_out, batch, cache, *, num_heads, rotation, qk_norm, temperature,
+                   value_mix=None, gates_out=None):
         """Encode positions of q and k, normalise, scale q, append k and v to the cache.
-        qkv [M, (nq + 2 nkv) hd] T -> q_out [M, nq hd] T; `cache` is a `LayerCache`.
+        qkv [M, >= (nq + 2 nkv) hd] T -> q_out [M, nq hd] T; `cache` is a `LayerCache`.
         `rotation`: a `parts.Rotation` or None; `qk_norm`: a `parts.QkNorm` or None (RMS norm of
         every q and k head, after the rotation unless it says before); `temperature`:
-        (floor, scale) or None: q *= ln(floor((pos + 1) / floor) + 1) * scale + 1."""
+        (floor, scale) or None: q *= ln(floor((pos + 1) / floor) + 1) * scale + 1.
+        `value_mix` = (other [M, *] T, column, head stride, value size, lam): element i < value size of kv head g's
+        value becomes (1 - lam) v + lam * other[m, column + g * head stride + i] before it is cached.
+        `gates_out` float32 [M, nq]: receives sigmoid(qkv[m, (nq + 2 nkv) hd + h]), the columns after the heads."""
         raise NotImplementedError
 
     def paged_attention(self, q, out, batch, cache, *, num_heads, window, softmax_scale, cache_settled=False,
-                        sink_logit=None):
+                        sink_logit=None, head_sinks=None, head_slopes=None, head_gates=None):
         """out[M, nq hd] = softmax(q K^T * scale over the visible cached keys) V.
-        `sink_logit`: the softmax's denominator also holds exp(sink_logit), a key without a value.
+        `sink_logit`: the softmax's denominator also holds exp(sink_logit), a key without a value;
+        `head_sinks` float32 [nq]: the same with a score of its own for every head.
+        `head_slopes` float32 [nq]: slope_h * (query position - key position) is taken off head h's scores.
+        `head_gates` float32 [M, nq]: head h's output for token m is multiplied by head_gates[m, h].
+        A cache with one plane (`cache.kv.shape[0] == 1`) holds keys only, and the value of a position is its key row.
         `cache_settled`: the caller promises that the cache rows of positions before each request's first
         token of this step were written by earlier steps (not by the one or two kernels launched just
         before this call), so a kernel may fetch them while the kernel before still runs."""
         raise NotImplementedError
 
+    # ---- attention through latents
+    def latent_prepare(self, down, cq_out, batch, cache, *, q_rank, kv_rank, rotation, q_gain, kv_gain, eps,
+                       num_gates=0, gates_out=None):
+        """One row of `down` (float32 [M, >= q_rank + kv_rank + rot + num_gates]) holds a token's query latent, its
+        key/value latent, the key part that all heads share and the gate columns.  cq_out [M, q_rank] (T) =
+        RMS norm of the query latent * q_gain; the cache row of the token's position becomes [RMS norm of the
+        key/value latent * kv_gain; the shared part rotated by `rotation` (neighbouring pairs, times its amplitude);
+        zeros up to the row's size]; gates_out [M, num_gates] float32 = sigmoid of the gate columns."""
+        raise NotImplementedError
+
+    def latent_queries(self, q, q_out, batch, *, num_heads, head_dim, kv_rank, rotation, rows_out, offsets_out):
+        """q [M, nq (head_dim + rot)] (T): every head's last `rot` elements are rotated (as in `latent_prepare`) into
+        q_out[m, h, kv_rank : kv_rank + rot], and q_out's elements behind them become zero (q_out [M, nq, row] T; its
+        first kv_rank elements are left for the product that follows).  Also lists the (token, head) rows head by
+        head: rows_out[h M + m] = m nq + h, offsets_out[h] = h M (int32 [nq M] and [nq + 1])."""
+        raise NotImplementedError
+
     # ---- mixture of experts
-    def moe_route(self, x, w_router, top_k, want_logits=False) -> Routing:
+    def moe_route(self, x, w_router, top_k, want_logits=False, scoring="sigmoid") -> Routing:
+        """Router logits in float32, the `top_k` largest per token (equal ones: the lower expert first), the
+        tokens sorted by expert for every choice slot.  `scoring` "sigmoid": the weight of a choice is the sigmoid
+        of its logit; "softmax_renorm": its share of the softmax over all experts, divided by the sum of the
+        chosen shares (+ 1e-20); `sorted_weights` is filled for it."""
         raise NotImplementedError
 
     # ---- sampling

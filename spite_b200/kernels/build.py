@@ -39,6 +39,7 @@ LIBRARIES = {
     "attention_rows": (["attention_rows.cu"], []),
     "attention_tc": (["attention_tc.cu"], []),
     "moe": (["moe.cu"], []),
+    "latent": (["latent.cu"], []),
     "sampling": (["sampling.cu"], []),
 }
 

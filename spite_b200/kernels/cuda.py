@@ -47,13 +47,32 @@ class QkPrepareParams(C.Structure):
                 ("q_gain", C.c_void_p), ("k_gain", C.c_void_p),
                 ("qk_norm_eps", C.c_float), ("norm_before_rotation", C.c_int), ("pairing", C.c_int),
                 ("rotary_dim", C.c_int), ("temperature_floor", C.c_int),
-                ("temperature_scale", C.c_float), ("num_heads", C.c_int), ("write_cache", C.c_int)]
+                ("temperature_scale", C.c_float), ("num_heads", C.c_int), ("write_cache", C.c_int),
+                ("qkv_stride", C.c_longlong), ("rot_amplitude", C.c_float),
+                ("v_other", C.c_void_p), ("v_other_stride", C.c_longlong), ("v_other_head", C.c_int),
+                ("v_mix_dim", C.c_int), ("v_mix", C.c_float), ("gates_out", C.c_void_p)]
 
 
 class AttentionParams(C.Structure):
     _fields_ = [("q", C.c_void_p), ("out", C.c_void_p), ("num_heads", C.c_int),
                 ("window_kind", C.c_int), ("window_size", C.c_int), ("softmax_scale", C.c_float),
-                ("has_sink", C.c_int), ("sink_logit", C.c_float)]
+                ("has_sink", C.c_int), ("sink_logit", C.c_float),
+                ("head_sinks", C.c_void_p), ("head_slopes", C.c_void_p), ("head_gates", C.c_void_p)]
+
+
+class LatentPrepareParams(C.Structure):
+    _fields_ = [("down", C.c_void_p), ("down_stride", C.c_longlong), ("cq_out", C.c_void_p),
+                ("q_gain", C.c_void_p), ("kv_gain", C.c_void_p), ("inv_freq", C.c_void_p),
+                ("rot_amplitude", C.c_float), ("eps", C.c_float),
+                ("q_rank", C.c_int), ("kv_rank", C.c_int), ("rot_dim", C.c_int), ("num_gates", C.c_int),
+                ("gates_out", C.c_void_p), ("write_cache", C.c_int)]
+
+
+class LatentQueryParams(C.Structure):
+    _fields_ = [("q", C.c_void_p), ("q_out", C.c_void_p), ("inv_freq", C.c_void_p), ("rot_amplitude", C.c_float),
+                ("num_heads", C.c_int), ("head_dim", C.c_int), ("rot_dim", C.c_int), ("kv_rank", C.c_int),
+                ("row", C.c_int), ("positions", C.c_void_p), ("n_tokens", C.c_int),
+                ("rows_out", C.c_void_p), ("offsets_out", C.c_void_p)]
 
 
 class AttnMmaExtra(C.Structure):
@@ -556,17 +575,33 @@ class CudaKernels(KernelSet):
                        activation=_ACTIVATION[activation])
         self._gemm(p, "grouped_linear_act", M, gather_src=x)
 
-    def grouped_linear_accumulate(self, a, w_down, sorted_rows, offsets, h):
+    def grouped_linear_accumulate(self, a, w_down, sorted_rows, offsets, h, *, row_scale=None):
         self._t(a, self.dtype, "a"); self._t(w_down, self.dtype, "w"); self._t(h, torch.float32, "h")
+        if row_scale is not None and self._t(row_scale, torch.float32, "row_scale").numel() != a.shape[0]:
+            raise KernelError("grouped_linear_accumulate: one scale per row of the sorted order")
         M, F = a.shape
         E, d, F2 = w_down.shape
         if F2 != F or h.shape[1] != d or offsets.numel() != E + 1 or sorted_rows.numel() != M:
             raise KernelError("grouped_linear_accumulate: shapes do not fit")
         p = GemmParams(A=a.data_ptr(), W=w_down.data_ptr(), C=h.data_ptr(), a_rows=None,
-                       c_rows=sorted_rows.data_ptr(), group_offsets=offsets.data_ptr(), row_scale=None,
+                       c_rows=sorted_rows.data_ptr(), group_offsets=offsets.data_ptr(), row_scale=_ptr(row_scale),
                        lda=F, ldc=d, w_group_stride=d * F, n_groups=E, M=M, N=d, K=F,
                        epilogue=EPI_ADD_F32, scale_by_a_row=0)
         self._gemm(p, "grouped_linear_accumulate", M)
+
+    def grouped_linear_rows(self, a, w, rows, offsets, out):
+        self._t(a, self.dtype, "a"); self._t(w, self.dtype, "w"); self._t(out, self.dtype, "out")
+        self._t(rows, torch.int32, "rows"); self._t(offsets, torch.int32, "offsets")
+        R, lda = a.shape
+        G, N, K = w.shape
+        if K > lda or out.shape[0] != R or N > out.shape[1] or offsets.numel() != G + 1 or rows.numel() > R:
+            raise KernelError("grouped_linear_rows: shapes do not fit")
+        M = rows.numel()
+        # the rows are gathered and scattered by the same list; columns beyond K of `a` and beyond N of `out` stay out
+        p = GemmParams(A=a.data_ptr(), W=w.data_ptr(), C=out.data_ptr(), a_rows=rows.data_ptr(), c_rows=rows.data_ptr(),
+                       group_offsets=offsets.data_ptr(), row_scale=None, lda=lda, ldc=out.shape[1],
+                       w_group_stride=N * K, n_groups=G, M=M, N=N, K=K, epilogue=EPI_STORE, scale_by_a_row=0)
+        self._gemm(p, "grouped_linear_rows", M, gather_src=a)
 
     # ------------------------------------------------------------------ attention
     def _step_tokens(self, batch, group):
@@ -575,16 +610,31 @@ class CudaKernels(KernelSet):
                           block_table=bt.data_ptr(), table_width=bt.shape[1], n_tokens=batch.n_tokens)
 
     def _paged(self, cache):
-        kv = cache.kv                       # [2, pages, nkv, page_size, hd]
+        kv = cache.kv                       # [planes, pages, nkv, page_size, hd]; one plane: the key rows are the values
         self._t(kv, self.dtype, "cache")
-        return PagedCache(kv=kv.data_ptr(), v_offset=kv.stride(0), n_pages=kv.shape[1],
+        return PagedCache(kv=kv.data_ptr(), v_offset=kv.stride(0) if kv.shape[0] == 2 else 0, n_pages=kv.shape[1],
                           page_size=kv.shape[3], num_kv_heads=kv.shape[2], head_dim=kv.shape[4])
 
-    def qk_prepare(self, qkv, q_out, batch, cache, *, num_heads, rotation, qk_norm, temperature):
+    def qk_prepare(self, qkv, q_out, batch, cache, *, num_heads, rotation, qk_norm, temperature,
+                   value_mix=None, gates_out=None):
         self._t(qkv, self.dtype, "qkv"); self._t(q_out, self.dtype, "q_out")
         head_dim = cache.kv.shape[4]
-        inv_freq, pairing, rotary_dim = None, 0, head_dim
+        if cache.kv.shape[0] != 2:
+            raise KernelError("qk_prepare appends keys and values: the cache needs both planes")
+        inv_freq, pairing, rotary_dim, amplitude = None, 0, head_dim, 1.0
+        v_other, v_stride, v_head, v_dim, v_lam = None, 0, 0, 0, 0.0
+        if value_mix is not None:
+            other, column, v_head, v_dim, v_lam = value_mix
+            self._t(other, self.dtype, "value_mix source")
+            if other.shape[0] != qkv.shape[0]:
+                raise KernelError("qk_prepare: the values to blend in belong to other tokens")
+            v_other, v_stride = other.data_ptr() + int(column) * other.element_size(), other.shape[1]
+        if gates_out is not None:
+            self._t(gates_out, torch.float32, "gates_out")
+            if tuple(gates_out.shape) != (qkv.shape[0], num_heads):
+                raise KernelError("qk_prepare: gates_out must be [tokens, heads]")
         if rotation is not None:
+            amplitude = float(rotation.amplitude)
             inv_freq = self._t(rotation.inv_freq, torch.float32, "inv_freq")
             pairing = {"neighbours": 0, "halves": 1}[rotation.pairing]
             rotary_dim = int(rotation.rotary_dim or head_dim)
@@ -602,7 +652,9 @@ class CudaKernels(KernelSet):
                             q_gain=_ptr(q_gain), k_gain=_ptr(k_gain), qk_norm_eps=eps,
                             norm_before_rotation=before, pairing=pairing, rotary_dim=rotary_dim,
                             temperature_floor=floor, temperature_scale=scale, num_heads=num_heads,
-                            write_cache=int(cache.write))
+                            write_cache=int(cache.write), qkv_stride=qkv.shape[1], rot_amplitude=amplitude,
+                            v_other=v_other, v_other_stride=v_stride, v_other_head=int(v_head), v_mix_dim=int(v_dim),
+                            v_mix=float(v_lam), gates_out=_ptr(gates_out))
         b, c = self._step_tokens(batch, cache.group), self._paged(cache)
         st = self._lib("attention").spite_qk_prepare(self._dt, C.byref(p), C.byref(b), C.byref(c), self._stream())
         self._count("attention", 1)
@@ -610,12 +662,20 @@ class CudaKernels(KernelSet):
 
 
     def paged_attention(self, q, out, batch, cache, *, num_heads, window, softmax_scale, cache_settled=False,
-                        sink_logit=None):
+                        sink_logit=None, head_sinks=None, head_slopes=None, head_gates=None):
         self._t(q, self.dtype, "q"); self._t(out, self.dtype, "out")
+        for name, t, n in (("head_sinks", head_sinks, num_heads), ("head_slopes", head_slopes, num_heads),
+                           ("head_gates", head_gates, q.shape[0] * num_heads)):
+            if t is not None and self._t(t, torch.float32, name).numel() != n:
+                raise KernelError(f"paged_attention: {name} has {t.numel()} elements, {n} are needed")
+        if not softmax_scale > 0:
+            raise KernelError("paged_attention: the score scale must be positive")
         p = AttentionParams(q=q.data_ptr(), out=out.data_ptr(), num_heads=num_heads,
                             window_kind=_WINDOW[window.kind], window_size=int(window.size),
-                            softmax_scale=float(softmax_scale), has_sink=int(sink_logit is not None),
-                            sink_logit=float(sink_logit or 0.0))
+                            softmax_scale=float(softmax_scale),
+                            has_sink=int(sink_logit is not None or head_sinks is not None),
+                            sink_logit=float(sink_logit or 0.0), head_sinks=_ptr(head_sinks),
+                            head_slopes=_ptr(head_slopes), head_gates=_ptr(head_gates))
         b, c = self._step_tokens(batch, cache.group), self._paged(cache)
         group = num_heads // c.num_kv_heads
         if (self.dtype == torch.bfloat16 and c.head_dim % 16 == 0 and c.head_dim <= 128 and group <= 16
@@ -731,8 +791,51 @@ class CudaKernels(KernelSet):
         self._count("attention_decode", 1)
         _check(st, "paged_attention (decode)")
 
+    # ------------------------------------------------------------------ attention through latents
+    def latent_prepare(self, down, cq_out, batch, cache, *, q_rank, kv_rank, rotation, q_gain, kv_gain, eps,
+                       num_gates=0, gates_out=None):
+        self._t(down, torch.float32, "down"); self._t(cq_out, self.dtype, "cq_out")
+        self._t(q_gain, torch.float32, "q_gain"); self._t(kv_gain, torch.float32, "kv_gain")
+        inv_freq = self._t(rotation.inv_freq, torch.float32, "inv_freq")
+        if rotation.pairing != "neighbours":
+            raise KernelError("latent_prepare rotates neighbouring pairs")
+        if q_gain.numel() != q_rank or kv_gain.numel() != kv_rank or tuple(cq_out.shape) != (down.shape[0], q_rank):
+            raise KernelError("latent_prepare: shapes do not fit")
+        if cache.kv.shape[0] != 1:
+            raise KernelError("latent_prepare writes one row per position: the cache has one plane")
+        if gates_out is not None and tuple(self._t(gates_out, torch.float32, "gates_out").shape) != (down.shape[0], num_gates):
+            raise KernelError("latent_prepare: gates_out must be [tokens, gates]")
+        p = LatentPrepareParams(down=down.data_ptr(), down_stride=down.shape[1], cq_out=cq_out.data_ptr(),
+                                q_gain=q_gain.data_ptr(), kv_gain=kv_gain.data_ptr(), inv_freq=inv_freq.data_ptr(),
+                                rot_amplitude=float(rotation.amplitude), eps=float(eps), q_rank=int(q_rank),
+                                kv_rank=int(kv_rank), rot_dim=2 * inv_freq.numel(), num_gates=int(num_gates),
+                                gates_out=_ptr(gates_out), write_cache=int(cache.write))
+        b, c = self._step_tokens(batch, cache.group), self._paged(cache)
+        st = self._lib("latent").spite_latent_prepare(self._dt, C.byref(p), C.byref(b), C.byref(c), self._stream())
+        self._count("latent", 1)
+        _check(st, "latent_prepare")
+
+    def latent_queries(self, q, q_out, batch, *, num_heads, head_dim, kv_rank, rotation, rows_out, offsets_out):
+        self._t(q, self.dtype, "q"); self._t(q_out, self.dtype, "q_out")
+        self._t(rows_out, torch.int32, "rows_out"); self._t(offsets_out, torch.int32, "offsets_out")
+        inv_freq = self._t(rotation.inv_freq, torch.float32, "inv_freq")
+        M, rot = q.shape[0], 2 * inv_freq.numel()
+        if q.shape[1] != num_heads * (head_dim + rot) or q_out.shape[0] != M or q_out.shape[1] % num_heads \
+                or rows_out.numel() != num_heads * M or offsets_out.numel() != num_heads + 1:
+            raise KernelError("latent_queries: shapes do not fit")
+        p = LatentQueryParams(q=q.data_ptr(), q_out=q_out.data_ptr(), inv_freq=inv_freq.data_ptr(),
+                              rot_amplitude=float(rotation.amplitude), num_heads=int(num_heads), head_dim=int(head_dim),
+                              rot_dim=rot, kv_rank=int(kv_rank), row=q_out.shape[1] // num_heads,
+                              positions=batch.positions.data_ptr(), n_tokens=M, rows_out=rows_out.data_ptr(),
+                              offsets_out=offsets_out.data_ptr())
+        st = self._lib("latent").spite_latent_queries(self._dt, C.byref(p), self._stream())
+        self._count("latent", 1)
+        _check(st, "latent_queries")
+
     # ------------------------------------------------------------------ mixture of experts
-    def moe_route(self, x, w_router, top_k, want_logits=False) -> Routing:
+    def moe_route(self, x, w_router, top_k, want_logits=False, scoring="sigmoid") -> Routing:
+        if scoring not in ("sigmoid", "softmax_renorm"):
+            raise KernelError(f"moe_route: unknown scoring {scoring!r}")
         self._t(x, self.dtype, "x"); self._t(w_router, torch.float32, "w_router")
         M, d = x.shape
         E = w_router.shape[0]
@@ -742,13 +845,16 @@ class CudaKernels(KernelSet):
         offsets = torch.empty((top_k, E + 1), dtype=torch.int32, device=dev)
         rows = torch.empty((top_k, M), dtype=torch.int32, device=dev)
         logits = torch.empty((M, E), dtype=torch.float32, device=dev)
+        renorm = scoring == "softmax_renorm"
+        sorted_w = torch.empty((top_k, M), dtype=torch.float32, device=dev) if renorm else None
         st = self._lib("moe").spite_moe_route(
             self._dt, C.c_void_p(x.data_ptr()), C.c_void_p(w_router.data_ptr()), M, d, E, top_k,
             C.c_void_p(ids.data_ptr()), C.c_void_p(wts.data_ptr()), C.c_void_p(_ptr(logits)),
-            C.c_void_p(offsets.data_ptr()), C.c_void_p(rows.data_ptr()), self._stream())
+            C.c_void_p(offsets.data_ptr()), C.c_void_p(rows.data_ptr()), int(renorm), C.c_void_p(_ptr(sorted_w)),
+            self._stream())
         self._count("moe", 2)
         _check(st, "moe_route")
-        return Routing(ids, wts, offsets, rows, logits if want_logits else None)
+        return Routing(ids, wts, offsets, rows, logits if want_logits else None, sorted_w)
 
     # ------------------------------------------------------------------ sampling
     def argmax(self, logits):

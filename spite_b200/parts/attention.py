@@ -3,8 +3,10 @@
 One part serves every attention layer: the window rule (all keys, the keys of
 the query's chunk, the last W keys), the position encoding, the per-head norm of
 q and k (after or before the rotation, with gains or without), the
-temperature factor, a value size that differs from the key size, and a sink in
-the softmax (an extra term exp(sink) in the sum, with nothing behind it) are constructor parameters.
+temperature factor, a value size that differs from the key size, a sink in
+the softmax (an extra term exp(sink) in the sum, with nothing behind it; one score for all heads or a learned
+one per head), a bias that grows with the distance between query and key, a gate on every head's output and the
+blending of the values with those of another layer are constructor parameters.
 
 Formulas: crates/spite-models/src/llama/llama4.rs:126-207 (projections, rotation
 then norm, temperature factor on layers without rotation, append to the cache,
@@ -30,10 +32,16 @@ class PagedAttention(Mixer):
     def __init__(self, ctx, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  position: PartSpec, window=("full", 0), qk_norm_eps=None, qk_norm_gain=False,
                  qk_norm_before_rotation=False, temperature_tuning=None, softmax_scale=None,
-                 value_dim=None, sink_logit=None):
+                 value_dim=None, sink_logit=None, head_sinks=False, distance_slopes=None, head_gate=False,
+                 value_mix=None):
         """`head_dim` is the size of a query and a key head, `value_dim` that of a value head (default: the
         same).  `sink_logit`, if given, is the score of a sink: a term exp(sink) in every softmax's sum that adds
-        nothing to the output, p_j = exp(s_j) / (exp(sink) + sum exp(s_j'))."""
+        nothing to the output, p_j = exp(s_j) / (exp(sink) + sum exp(s_j')); with `head_sinks` the score is a
+        learned parameter per head (`sinks` [heads]).  `distance_slopes` (one number per head): slope_h * (i - j)
+        is taken off the score of query position i and key position j.  `head_gate`: head h's output is multiplied by
+        sigmoid(w_h . x), w the rows of `gate_proj` [heads, hidden], x the mixer's input.  `value_mix`: "source"
+        marks the layer whose values of the step's tokens later layers blend in; "blend" makes this layer's
+        values (1 - lam) v + lam v_source before they are cached, lam the scalar parameter `value_mix`."""
         super().__init__(ctx)
         if num_heads % num_kv_heads:
             raise ConfigError(f"{num_heads} query heads cannot share {num_kv_heads} kv heads evenly")
@@ -45,6 +53,18 @@ class PagedAttention(Mixer):
         if self.vd < 1 or self.vd > 256:
             raise ConfigError(f"value_dim {self.vd} must lie in 1..256")
         self.sink_logit = None if sink_logit is None else float(sink_logit)
+        self.has_head_sinks = bool(head_sinks)
+        if self.has_head_sinks and self.sink_logit is not None:
+            raise ConfigError("a sink is either one score for all heads or a learned one per head")
+        if distance_slopes is not None and len(distance_slopes) != num_heads:
+            raise ConfigError(f"{len(distance_slopes)} distance slopes for {num_heads} heads")
+        self._slopes = None if distance_slopes is None else torch.tensor(
+            [float(s) for s in distance_slopes], dtype=torch.float64).to(torch.float32).to(ctx.device)
+        self.head_gate = bool(head_gate)
+        if value_mix not in (None, "source", "blend"):
+            raise ConfigError(f"value_mix {value_mix!r} is unknown (source, blend)")
+        self.value_mix = value_mix
+        self.head_sinks = self.value_lambda = None
         self.window = window if isinstance(window, Window) else Window(window[0], int(window[1]))
         self.position = build_part("position", position, ctx)
         # Keys and values share the cache's pages and the attention kernels' tiles, which have one row size.  Where
@@ -86,6 +106,12 @@ class PagedAttention(Mixer):
                  "v_proj": ParamSpec((nkv * vd, d)), "o_proj": ParamSpec((d, nq * vd))}
         if self.qk_norm_gain:
             specs.update({"q_norm": ParamSpec((kd,), "ones"), "k_norm": ParamSpec((kd,), "ones")})
+        if self.has_head_sinks:
+            specs["sinks"] = ParamSpec((nq,))
+        if self.head_gate:
+            specs["gate_proj"] = ParamSpec((nq, d))
+        if self.value_mix:
+            specs["value_mix"] = ParamSpec(())          # (the source layer's own is in the file too, and unused)
         return specs
 
     def _pad_heads(self, w, heads, size):
@@ -99,9 +125,18 @@ class PagedAttention(Mixer):
     def bind(self, params):
         dt = self.ctx.dtype
         # q, k and v rows in one matrix: one product per layer instead of three
-        self.wqkv = torch.cat([self._pad_heads(params["q_proj"].to(dt), self.nq, self.kd),
-                               self._pad_heads(params["k_proj"].to(dt), self.nkv, self.kd),
-                               self._pad_heads(params["v_proj"].to(dt), self.nkv, self.vd)], 0).contiguous()
+        rows = [self._pad_heads(params["q_proj"].to(dt), self.nq, self.kd),
+                self._pad_heads(params["k_proj"].to(dt), self.nkv, self.kd),
+                self._pad_heads(params["v_proj"].to(dt), self.nkv, self.vd)]
+        if self.head_gate:
+            # the gates' rows ride in the same product: one more column per head, then zero rows up to a multiple of 8
+            g = params["gate_proj"].to(dt)
+            rows += [g, torch.zeros((-self.nq % 8, self.d), dtype=dt, device=g.device)]
+        self.wqkv = torch.cat(rows, 0).contiguous()
+        if self.has_head_sinks:
+            self.head_sinks = params["sinks"].to(torch.float32).contiguous()
+        if self.value_mix == "blend":
+            self.value_lambda = float(params["value_mix"].to(torch.float32))
         # the output projection's columns, head by head, with zero columns for the padding
         self.wo = self._pad_heads(params["o_proj"].to(dt).t().contiguous(), self.nq, self.vd).t().contiguous()
         if self.qk_norm_gain:
@@ -118,14 +153,35 @@ class PagedAttention(Mixer):
     def forward(self, x, h, batch, cache):
         M = x.shape[0]
         k = self.k
-        qkv = torch.empty((M, (self.nq + 2 * self.nkv) * self.hd), dtype=x.dtype, device=x.device)
+        qkv = torch.empty((M, self.wqkv.shape[0]), dtype=x.dtype, device=x.device)
         k.linear(x, self.wqkv, qkv)
         q = torch.empty((M, self.nq * self.hd), dtype=x.dtype, device=x.device)
+        extra = {}
+        gates = None
+        if self.head_gate:
+            gates = extra["gates_out"] = torch.empty((M, self.nq), dtype=torch.float32, device=x.device)
+        v_column = (self.nq + self.nkv) * self.hd
+        if self.value_mix == "source":
+            # the step's values as this layer projects them, for the layers that blend them in (the step keeps
+            # the product's output alive until it ends)
+            batch.shared["value_mix_source"] = (qkv, v_column, self.hd, self.nkv)
+        elif self.value_mix == "blend":
+            src = batch.shared.get("value_mix_source")
+            if src is None or src[3] != self.nkv:
+                raise ConfigError("a layer blends values in, but no layer before it in the run order is their source")
+            extra["value_mix"] = (src[0], src[1], src[2], self.vd, self.value_lambda)
         k.qk_prepare(qkv, q, batch, cache, num_heads=self.nq, rotation=self.position.rotation(),
-                     qk_norm=self.qk_norm, temperature=self.temperature)
+                     qk_norm=self.qk_norm, temperature=self.temperature, **extra)
         o = torch.empty_like(q)
         # keys and values of earlier positions were cached by earlier steps; this step's own were written by
         # the prepare kernel just before, which is what the attention kernel waits for
+        more = {}
+        if self.head_sinks is not None:
+            more["head_sinks"] = self.head_sinks
+        if self._slopes is not None:
+            more["head_slopes"] = self._slopes
+        if gates is not None:
+            more["head_gates"] = gates
         k.paged_attention(q, o, batch, cache, num_heads=self.nq, window=self.window,
-                          softmax_scale=self.softmax_scale, cache_settled=True, sink_logit=self.sink_logit)
+                          softmax_scale=self.softmax_scale, cache_settled=True, sink_logit=self.sink_logit, **more)
         k.linear(o, self.wo, h, accumulate=True)

@@ -128,10 +128,12 @@ class Rotation:
     """How a position part wants q and k encoded; the mixer's prepare kernel does it.
     Pair i of a head is rotated by position * inv_freq[i].  `pairing` says which two elements
     pair i is: "neighbours" (2i, 2i+1) or "halves" (i, i + rotary_dim/2).  Only the first
-    `rotary_dim` elements of a head rotate (None: all of them)."""
+    `rotary_dim` elements of a head rotate (None: all of them).  `amplitude` multiplies both cos and
+    sin (the rotated pair grows by it)."""
     inv_freq: torch.Tensor              # float32 [rotary_dim / 2] on the device
     pairing: str = "neighbours"
     rotary_dim: Optional[int] = None
+    amplitude: float = 1.0
 
     def __post_init__(self):
         if self.pairing not in ("neighbours", "halves"):

@@ -169,3 +169,87 @@ class MoESigmoidPrescaled(FeedForward):
         if side is None:
             side = _SIDE_STREAMS[x.device] = torch.cuda.Stream(device=x.device)
         return side
+
+
+@register_feed_forward("dense_activation")
+class DenseActivation(FeedForward):
+    """h += down( act(up x) ) without a gate; `activation` "relu2": act(z) = relu(z)^2, applied to the float32
+    sums of the first product before they are rounded."""
+    graph_safe = True
+    kernel_libraries = ("gemm_simt",)
+
+    ACTIVATIONS = ("relu2",)
+
+    def __init__(self, ctx, hidden_size: int, intermediate_size: int, activation: str = "relu2"):
+        super().__init__(ctx)
+        if activation not in self.ACTIVATIONS:
+            raise ConfigError(f"unknown activation {activation!r}; known: {', '.join(self.ACTIVATIONS)}")
+        self.d, self.f, self.activation = int(hidden_size), int(intermediate_size), activation
+        self.w_up = self.w_down = None
+
+    def param_specs(self):
+        return {"up_proj": ParamSpec((self.f, self.d)), "down_proj": ParamSpec((self.d, self.f))}
+
+    def bind(self, params):
+        dt = self.ctx.dtype
+        self.w_up = params["up_proj"].to(dt).contiguous()
+        self.w_down = params["down_proj"].to(dt).contiguous()
+
+    def weight_bytes(self):
+        return (self.w_up.numel() + self.w_down.numel()) * self.w_down.element_size()
+
+    def forward(self, x, h, batch):
+        a = torch.empty((x.shape[0], self.f), dtype=x.dtype, device=x.device)
+        self.k.linear(x, self.w_up, a, activation=self.activation)
+        self.k.linear(a, self.w_down, h, accumulate=True)
+
+
+@register_feed_forward("moe_softmax_topk")
+class MoESoftmaxTopK(FeedForward):
+    """Mixture of gated experts whose router weights the experts' outputs:
+
+        s = softmax(W_r x) over all experts (float32);  the `top_k` largest are chosen;
+        w_e = s_e / (sum of the chosen s + 1e-20);  h += sum_e w_e * down_e( silu(gate_e x) * (up_e x) )
+
+    The weight multiplies the float32 sums of the expert's last product as they are added to the residual
+    stream, so no rounded intermediate carries it."""
+    graph_safe = True
+    kernel_libraries = ("gemm_simt", "moe")
+
+    def __init__(self, ctx, hidden_size: int, num_experts: int, top_k: int, expert_size: int):
+        super().__init__(ctx)
+        if not 1 <= top_k <= num_experts:
+            raise ConfigError(f"top_k {top_k} must lie in 1..{num_experts}")
+        self.d, self.E, self.top_k, self.f = int(hidden_size), int(num_experts), int(top_k), int(expert_size)
+        self.router = self.w_gate_up = self.w_down = None
+        self.keep_router_logits = False      # `last_routing.logits` [tokens, experts] stays readable after a forward
+
+    def param_specs(self):
+        d, E, f = self.d, self.E, self.f
+        return {"router": ParamSpec((E, d)), "experts_gate": ParamSpec((E, f, d)), "experts_up": ParamSpec((E, f, d)),
+                "experts_down": ParamSpec((E, d, f))}
+
+    def bind(self, params):
+        dt = self.ctx.dtype
+        self.router = params["router"].to(torch.float32).contiguous()        # float32 sums of float32 weights
+        self.w_gate_up = torch.cat([params["experts_gate"].to(dt), params["experts_up"].to(dt)], 1).contiguous()
+        self.w_down = params["experts_down"].to(dt).contiguous()
+
+    def weight_bytes(self):
+        return (self.w_gate_up.numel() + self.w_down.numel()) * self.w_down.element_size() + self.router.numel() * 4
+
+    def active_weight_bytes(self, n_distinct_experts: float) -> int:
+        """Bytes a step reads when its tokens use `n_distinct_experts` experts (a mean over steps may be fractional)."""
+        per = 3 * self.f * self.d * self.w_down.element_size()
+        return int(per * n_distinct_experts) + self.router.numel() * 4
+
+    def forward(self, x, h, batch):
+        k = self.k
+        M = x.shape[0]
+        routing = k.moe_route(x, self.router, self.top_k, want_logits=self.keep_router_logits, scoring="softmax_renorm")
+        self.last_routing = routing
+        for slot in range(self.top_k):
+            a = torch.empty((M, self.f), dtype=x.dtype, device=x.device)
+            k.grouped_linear_swiglu(x, self.w_gate_up, routing.sorted_rows[slot], routing.offsets[slot], None, a)
+            k.grouped_linear_accumulate(a, self.w_down, routing.sorted_rows[slot], routing.offsets[slot], h,
+                                        row_scale=routing.sorted_weights[slot])

@@ -64,3 +64,46 @@ class NoPosition(PositionEncoding):
 
     def rotation(self):
         return None
+
+
+def yarn_frequencies(rotary_dim: int, theta: float, scaling: dict | None):
+    """(frequencies, amplitude) of a rotation whose long wavelengths are stretched (the YaRN rule).
+
+    f_i = theta^(-2i/dims).  With `scaling` = {factor, original, fast, slow}: the pair index at which a
+    wavelength makes t turns over the original context is dim(t) = dims ln(original / (2 pi t)) / (2 ln theta);
+    lo = max(floor(dim(fast)), 0), hi = min(ceil(dim(slow)), dims - 1); pairs below lo keep f_i, pairs above hi get
+    f_i / factor, between them the two are blended linearly in the pair index (an empty band is guarded by a
+    width of at least 0.001).  The amplitude 0.1 ln(factor) + 1 multiplies cos and sin."""
+    half = rotary_dim // 2
+    freqs = [theta ** (-2.0 * i / rotary_dim) for i in range(half)]
+    if not scaling:
+        return freqs, 1.0
+    factor, orig = float(scaling["factor"]), float(scaling["original"])
+
+    def dim_of(turns):
+        return rotary_dim * math.log(orig / (2.0 * math.pi * turns)) / (2.0 * math.log(theta))
+    lo = max(math.floor(dim_of(float(scaling["fast"]))), 0)
+    hi = min(math.ceil(dim_of(float(scaling["slow"]))), rotary_dim - 1)
+    out = []
+    for i, f in enumerate(freqs):
+        ramp = min(1.0, max(0.0, (i - lo) / max(hi - lo, 0.001)))
+        out.append(f / factor * ramp + f * (1.0 - ramp))
+    return out, 0.1 * math.log(factor) + 1.0
+
+
+@register_position("rotary_yarn")
+class RotaryYarn(PositionEncoding):
+    """Rotation of neighbouring pairs (2i, 2i+1) of the first `rotary_dim` elements, wavelengths stretched by
+    `scaling` (None: the plain frequencies, amplitude one)."""
+    graph_safe = True
+
+    def __init__(self, ctx, rotary_dim: int, theta: float, scaling: dict | None = None):
+        super().__init__(ctx)
+        if rotary_dim % 2 or rotary_dim < 2:
+            raise ConfigError("a rotation needs an even number of elements")
+        f, amplitude = yarn_frequencies(int(rotary_dim), float(theta), scaling)
+        self._rotation = Rotation(torch.tensor(f, dtype=torch.float64).to(torch.float32).to(ctx.device), "neighbours",
+                                  int(rotary_dim), float(amplitude))
+
+    def rotation(self):
+        return self._rotation

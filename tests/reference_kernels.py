@@ -106,7 +106,7 @@ class TorchReferenceKernels(KernelSet):
                 y = y * row_scale[tok].to(self.acc)[:, None]
             out[lo:hi] = (torch.relu(y) ** 2).to(out.dtype)
 
-    def grouped_linear_accumulate(self, a, w_down, sorted_rows, offsets, h):
+    def grouped_linear_accumulate(self, a, w_down, sorted_rows, offsets, h, *, row_scale=None):
         E = w_down.shape[0]
         off = offsets.tolist()
         rows = sorted_rows.long()
@@ -114,17 +114,39 @@ class TorchReferenceKernels(KernelSet):
             lo, hi = off[e], off[e + 1]
             if hi == lo:
                 continue
-            h[rows[lo:hi]] += self._mm(a[lo:hi], w_down[e]).to(h.dtype)
+            y = self._mm(a[lo:hi], w_down[e])
+            if row_scale is not None:
+                y = y * row_scale[lo:hi].to(self.acc)[:, None]
+            h[rows[lo:hi]] += y.to(h.dtype)
+
+    def grouped_linear_rows(self, a, w, rows, offsets, out):
+        G, N, K = w.shape
+        off = offsets.tolist()
+        idx = rows.long()
+        for g in range(G):
+            r = idx[off[g]:off[g + 1]]
+            if r.numel():
+                out[r, :N] = self._mm(a[r, :K], w[g]).to(out.dtype)
 
     # ---- attention
-    def qk_prepare(self, qkv, q_out, batch, cache, *, num_heads, rotation, qk_norm, temperature):
+    def qk_prepare(self, qkv, q_out, batch, cache, *, num_heads, rotation, qk_norm, temperature,
+                   value_mix=None, gates_out=None):
         kv = cache.kv
         nkv, P, hd = kv.shape[2], kv.shape[3], kv.shape[4]
         nq = num_heads
         M = qkv.shape[0]
-        x = qkv.to(self.acc).view(M, nq + 2 * nkv, hd)
+        cols = (nq + 2 * nkv) * hd
+        x = qkv[:, :cols].to(self.acc).reshape(M, nq + 2 * nkv, hd)
         q, k, v = x[:, :nq], x[:, nq:nq + nkv], x[:, nq + nkv:]
         pos = batch.positions.long()
+        if gates_out is not None:
+            gates_out.copy_(torch.sigmoid(qkv[:, cols:cols + nq].to(torch.float32)))
+        if value_mix is not None:
+            other, col, stride, vd, lam = value_mix
+            v = v.clone()
+            for g in range(nkv):
+                o = other[:, col + g * stride: col + g * stride + vd].to(self.acc)
+                v[:, g, :vd] = (1.0 - lam) * v[:, g, :vd] + lam * o
 
         def norm(t, gain):
             t = t * (1.0 / torch.sqrt(t.pow(2).mean(-1, keepdim=True) + qk_norm.eps))
@@ -136,7 +158,7 @@ class TorchReferenceKernels(KernelSet):
             inv_freq = rotation.inv_freq.to(q.device)
             rd = rotation.rotary_dim or hd
             ang = (pos.to(torch.float32)[:, None] * inv_freq[None, :].to(torch.float32)).to(self.acc)
-            cos, sin = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+            cos, sin = torch.cos(ang)[:, None, :] * rotation.amplitude, torch.sin(ang)[:, None, :] * rotation.amplitude
 
             def rot(t):
                 o = t.clone()
@@ -167,8 +189,58 @@ class TorchReferenceKernels(KernelSet):
                 kv[0, page, :, p % P, :] = k[t].to(kv.dtype)
                 kv[1, page, :, p % P, :] = v[t].to(kv.dtype)
 
+    def _rotate_pairs(self, t, pos, rotation):
+        """t [M, ..., rot]: neighbouring pairs turn by pos * inv_freq, times the amplitude."""
+        ang = (pos.to(torch.float32)[:, None] * rotation.inv_freq.to(t.device, torch.float32)[None, :]).to(self.acc)
+        shape = [t.shape[0]] + [1] * (t.dim() - 2) + [ang.shape[1]]
+        cos, sin = (torch.cos(ang) * rotation.amplitude).view(shape), (torch.sin(ang) * rotation.amplitude).view(shape)
+        a, b = t[..., 0::2], t[..., 1::2]
+        o = torch.empty_like(t)
+        o[..., 0::2] = a * cos - b * sin
+        o[..., 1::2] = a * sin + b * cos
+        return o
+
+    def latent_prepare(self, down, cq_out, batch, cache, *, q_rank, kv_rank, rotation, q_gain, kv_gain, eps,
+                       num_gates=0, gates_out=None):
+        kv = cache.kv
+        P, row = kv.shape[3], kv.shape[4]
+        rot = rotation.inv_freq.numel() * 2
+        x = down.to(self.acc)
+        pos = batch.positions.long()
+
+        def norm(t, gain):
+            return t * (1.0 / torch.sqrt(t.pow(2).mean(-1, keepdim=True) + eps)) * gain.to(self.acc)
+        cq_out.copy_(norm(x[:, :q_rank], q_gain).to(cq_out.dtype))
+        c = norm(x[:, q_rank:q_rank + kv_rank], kv_gain)
+        kr = self._rotate_pairs(x[:, q_rank + kv_rank:q_rank + kv_rank + rot], pos, rotation)
+        if gates_out is not None:
+            g0 = q_rank + kv_rank + rot
+            gates_out.copy_(torch.sigmoid(down[:, g0:g0 + num_gates].to(torch.float32)))
+        if cache.write:
+            bt = batch.block_tables[cache.group]
+            seg = batch.seg_of_token.long()
+            for t in range(x.shape[0]):
+                p = int(pos[t])
+                page = int(bt[seg[t], p // P])
+                assert page >= 0, "write into a page that is not held"
+                kv[0, page, 0, p % P, :] = 0
+                kv[0, page, 0, p % P, :kv_rank] = c[t].to(kv.dtype)
+                kv[0, page, 0, p % P, kv_rank:kv_rank + rot] = kr[t].to(kv.dtype)
+
+    def latent_queries(self, q, q_out, batch, *, num_heads, head_dim, kv_rank, rotation, rows_out, offsets_out):
+        M = q.shape[0]
+        rot = rotation.inv_freq.numel() * 2
+        qv = q.to(self.acc).view(M, num_heads, head_dim + rot)
+        out = q_out.view(M, num_heads, -1)
+        out[:, :, kv_rank:] = 0
+        out[:, :, kv_rank:kv_rank + rot] = self._rotate_pairs(qv[:, :, head_dim:], batch.positions.long(), rotation).to(out.dtype)
+        m = torch.arange(M, dtype=torch.int32, device=q.device)
+        for h in range(num_heads):
+            rows_out[h * M:(h + 1) * M] = m * num_heads + h
+        offsets_out.copy_(torch.arange(num_heads + 1, dtype=torch.int32, device=q.device) * M)
+
     def paged_attention(self, q, out, batch, cache, *, num_heads, window, softmax_scale, cache_settled=False,
-                        sink_logit=None):
+                        sink_logit=None, head_sinks=None, head_slopes=None, head_gates=None):
         kv = cache.kv
         nkv, P, hd = kv.shape[2], kv.shape[3], kv.shape[4]
         nq = num_heads
@@ -185,21 +257,32 @@ class TorchReferenceKernels(KernelSet):
             pages = bt[seg[t]].long()[torch.div(js, P, rounding_mode="floor")]
             assert bool((pages >= 0).all()), "read from a page that was given back"
             K = kv[0, pages, :, js % P, :].to(self.acc)          # [n, nkv, hd]
-            V = kv[1, pages, :, js % P, :].to(self.acc)
+            V = kv[kv.shape[0] - 1, pages, :, js % P, :].to(self.acc)     # (one plane: the key rows are the values)
             for h in range(nq):
                 s = (K[:, h // group, :] @ qf[t, h]) * softmax_scale
-                if sink_logit is None:
+                if head_slopes is not None:
+                    s = s - float(head_slopes[h]) * (p - js).to(self.acc)
+                sink = sink_logit if head_sinks is None else float(head_sinks[h])
+                if sink is None:
                     w = torch.softmax(s, dim=0)
                 else:                                            # a key of that score and no value
-                    w = torch.softmax(torch.cat([s, s.new_tensor([sink_logit])]), dim=0)[:-1]
-                out[t, h * hd:(h + 1) * hd] = (w @ V[:, h // group, :]).to(out.dtype)
+                    w = torch.softmax(torch.cat([s, s.new_tensor([sink])]), dim=0)[:-1]
+                o = w @ V[:, h // group, :]
+                if head_gates is not None:
+                    o = o * head_gates[t, h].to(self.acc)
+                out[t, h * hd:(h + 1) * hd] = o.to(out.dtype)
 
     # ---- mixture of experts
-    def moe_route(self, x, w_router, top_k, want_logits=False) -> Routing:
+    def moe_route(self, x, w_router, top_k, want_logits=False, scoring="sigmoid") -> Routing:
         logits = (x.to(torch.float32) @ w_router.to(torch.float32).T)
         order = torch.sort(logits, dim=-1, descending=True, stable=True)
         ids = order.indices[:, :top_k].T.contiguous().to(torch.int32)        # [k, M]
-        w = (1.0 / (1.0 + torch.exp(-order.values[:, :top_k]))).T.contiguous()
+        if scoring == "sigmoid":
+            w = (1.0 / (1.0 + torch.exp(-order.values[:, :top_k]))).T.contiguous()
+        else:
+            assert scoring == "softmax_renorm"
+            share = torch.softmax(logits, -1).gather(1, order.indices[:, :top_k])
+            w = (share / (share.sum(-1, keepdim=True) + 1e-20)).T.contiguous()
         M, E = logits.shape
         offsets = torch.zeros((top_k, E + 1), dtype=torch.int32, device=x.device)
         rows = torch.zeros((top_k, M), dtype=torch.int32, device=x.device)
@@ -208,7 +291,8 @@ class TorchReferenceKernels(KernelSet):
             rows[s] = srt.indices.to(torch.int32)
             counts = torch.bincount(ids[s].long(), minlength=E)
             offsets[s, 1:] = torch.cumsum(counts, 0).to(torch.int32)
-        return Routing(ids, w, offsets, rows, logits if want_logits else None)
+        sorted_w = torch.stack([w[s][rows[s].long()] for s in range(top_k)], 0)
+        return Routing(ids, w, offsets, rows, logits if want_logits else None, sorted_w)
 
     # ---- sampling
     def argmax(self, logits):
