@@ -111,7 +111,7 @@ def save_file(tensors: dict[str, torch.Tensor], path, metadata: dict | None = No
         fh.write(blob)
         for name in order:
             t = tensors[name].detach().cpu().contiguous()
-            fh.write(t.view(torch.uint8).numpy().tobytes() if t.numel() else b"")
+            fh.write(t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b"")     # (a scalar has no axis to view)
 
 
 def open_checkpoint(folder) -> list[SafetensorsFile]:

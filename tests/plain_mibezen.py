@@ -126,11 +126,11 @@ def latent_attention(h, W, m, eps):
 
 def chunk_attention(h, W, m, v_first, lam):
     """Grouped-query attention without rotation: a bias that grows with distance, sight limited to the query's
-    own chunk, a learned sink per head in the softmax's denominator, values mixed with those of the first such
+    own chunk (if the layer has a mask), a learned sink per head in the softmax's denominator, values mixed with those of the first such
     layer.  Returns (output, the values this layer used)."""
     T = h.shape[0]
     H, G, d, dv = int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"])
-    size = int(m["mask"]["size"])
+    size = int(m["mask"]["size"]) if m.get("mask") else T         # without a mask the whole sequence is one chunk
     q = (h @ W["q"].T).reshape(T, H, d)
     k = (h @ W["k"].T).reshape(T, G, d)
     v = (h @ W["v"].T).reshape(T, G, dv)
