@@ -12,6 +12,7 @@ Two further workloads print a line of the same kind (they are extra modes; the d
                                          # 64 requests with prompts of 16 to 4,096 tokens through the scheduler
     python bench.py --config long        # Scout layer shapes, 8 layers: a prompt of 131,072 tokens in portions of
                                          # 8,192, then 256 decode steps at batch 1 and at batch 4
+    python bench.py --config mibezen     # the Mibezen design beside Llama 4 at equal layer sizes, measured the same way
     python bench.py --config sezazen     # the Sezazen design beside Llama 4 at equal layer sizes (three sizes): prefill
                                          # of 2,048 tokens and decode at batch 1 and 8, each with its roofline fraction
 """
@@ -315,11 +316,34 @@ def design_configs(size, runs=8):
     return sez, llama
 
 
+def mibezen_configs(size, runs=8):
+    """A Mibezen model of eight layers (attention with a dense feed-forward, three latent-attention layers with
+    experts, attention with experts that blends the first layer's values in, three more latent layers) and a Llama 4
+    model of eight layers with the same width, experts and vocabulary, whose attention has the heads of Mibezen's
+    attention layers.  A latent row is kv_rank + rot_dim = 128 elements, the largest the tensor-core attention
+    kernels take; a chunk is longer than the measured contexts, so every earlier key is read."""
+    name, d, nq, nkv, kd, vd, E, top, f, fs, fd, V = size
+    att = lambda mix: {"heads": nq, "kv_heads": nkv, "dim": kd, "vdim": kd, "scale": kd ** -0.5, "mask": {"size": 8192}, "v_mix": mix}
+    lat = {"heads": 16, "dim": 64, "rot_dim": 32, "vdim": 64, "q_rank": d // 4, "kv_rank": 96, "scale": 96 ** -0.5,
+           "rot": {"base": 10000.0, "dims": 32, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    moe = {"kind": "moe", "expert": {"ff": f}, "router": {"experts": E, "top": top}}
+    L = lambda t, m, mlp: {"type": t, "mixer": m, "mlp": mlp}
+    mib = {"architecture": "Mibezen", "vocab": V, "width": d, "max_positions": 8192, "norm": {"eps": 1e-5}, "logit_softcap": 30.0,
+           "layers": [L("attention", att(True), {"kind": "dense", "ff": fd})] + [L("latent_attention", lat, moe)] * 3 +
+                     [L("attention", att(True), moe)] + [L("latent_attention", lat, moe)] * 3}
+    llama = dict(SCOUT, num_hidden_layers=runs, hidden_size=d, num_attention_heads=nq, num_key_value_heads=nkv,
+                 head_dim=kd, num_local_experts=E, num_experts_per_tok=top, intermediate_size=f,
+                 intermediate_size_mlp=fd, moe_layers=list(range(1, runs)), vocab_size=V, tie_word_embeddings=True,
+                 max_position_embeddings=8192)
+    return mib, llama
+
+
 def design_work(model, T, contexts):
     """(flops of a prompt of T tokens, bytes a decode step over `contexts` must read), from the parts' own sizes
     as the design states them (no padding): every layer run reads its weights once; experts by the tokens' draw."""
     from spite_b200.config.specs import LayerCall
-    from spite_b200.parts.feedforward import MoESigmoidPrescaled
+    from spite_b200.parts.feedforward import DenseActivation, MoESigmoidPrescaled, MoESoftmaxTopK
+    from spite_b200.parts.latent import LatentAttention
     es, p = 2, model.plan
     flops, nbytes = 2 * p.hidden_size * p.vocab_size, p.vocab_size * p.hidden_size * es
     for j in model.junctions:
@@ -329,13 +353,28 @@ def design_work(model, T, contexts):
     for call in p.layer_calls():
         blk = model.blocks[call.layer]
         m, d = blk.mixer, p.hidden_size
-        w = d * (m.nq * m.kd + m.nkv * m.kd + m.nkv * m.vd) + m.nq * m.vd * d
-        flops += 2 * T * w + 2 * m.nq * (m.kd + m.vd) * T * (T + 1) // 2
-        nbytes += w * es + sum(c * m.nkv * (m.kd + m.vd) * es for c in contexts)
+        if isinstance(m, LatentAttention):
+            # the design's own count: keys and values of every head expanded from the latents (the products with the
+            # heads' matrices are part of w), scores over head_dim + rotary_dim, values over value_dim; a decode step
+            # reads one row of kv_rank + rotary_dim elements per cached position
+            w = d * (m.rq + m.rkv + m.dr + m.nq) + m.rq * m.nq * (m.dn + m.dr) + m.nq * (m.dn + m.dv) * m.rkv + m.nq * m.dv * d
+            flops += 2 * T * w + 2 * m.nq * (m.dn + m.dr + m.dv) * T * (T + 1) // 2
+            nbytes += w * es + sum(c * (m.rkv + m.dr) * es for c in contexts)
+        else:
+            w = d * (m.nq * m.kd + m.nkv * m.kd + m.nkv * m.vd) + m.nq * m.vd * d + (m.nq * d if getattr(m, "head_gate", False) else 0)
+            flops += 2 * T * w + 2 * m.nq * (m.kd + m.vd) * T * (T + 1) // 2
+            nbytes += w * es + sum(c * m.nkv * (m.kd + m.vd) * es for c in contexts)
         f = blk.ffn
         if f is None:
             continue
-        if isinstance(f, MoESigmoidPrescaled):
+        if isinstance(f, MoESoftmaxTopK):
+            used = torch_unique(f)
+            flops += 2 * T * d * (f.E + 3 * f.top_k * f.f)
+            nbytes += 3 * d * used * f.f * es + f.E * d * 4
+        elif isinstance(f, DenseActivation):
+            flops += 2 * T * 2 * d * f.f
+            nbytes += 2 * d * f.f * es
+        elif isinstance(f, MoESigmoidPrescaled):
             mats = 3 if f.gated else 2
             used = torch_unique(f)
             flops += 2 * T * d * (f.E + mats * (f.top_k * f.f + f.fs))
@@ -353,9 +392,12 @@ def torch_unique(ffn):
 
 
 def run_sezazen(args):
-    """The Sezazen design beside the closest existing one, Llama 4, at equal layer sizes: prefill of 2,048 tokens
-    (a fraction of the sustained bf16 rate) and decode at batch 1 and 8 with 2,048 cached tokens (a fraction of
-    the copy bandwidth).  One JSON line; `value` is Sezazen's decode rate at batch 8 at the first size."""
+    """A design (`--config sezazen` or `mibezen`) beside the closest existing one, Llama 4, at equal layer sizes:
+    prefill of 2,048 tokens (a fraction of the sustained bf16 rate) and decode at batch 1 and 8 with 2,048 cached
+    tokens (a fraction of the copy bandwidth).  One JSON line; `value` is the design's decode rate at batch 8 at
+    the first size."""
+    design = args.config
+    configs_of = design_configs if design == "sezazen" else mibezen_configs
     import torch
     from spite_b200.config import config_from_dict
     from spite_b200.engine import Engine, Model, StepEntry
@@ -423,17 +465,17 @@ def run_sezazen(args):
         torch.cuda.empty_cache()
         return res
 
-    sizes = [s for s in DESIGN_SIZES if args.size in (None, s[0])]
+    sizes = [s for s in (DESIGN_SIZES if design == "sezazen" else DESIGN_SIZES[:2]) if args.size in (None, s[0])]
     with clocks:
         for size in sizes:
-            sez, llama = design_configs(size)
-            out[size[0]] = {name: measure(cfgd) for name, cfgd in (("sezazen", sez), ("llama4", llama))
+            sez, llama = configs_of(size)
+            out[size[0]] = {name: measure(cfgd) for name, cfgd in ((design, sez), ("llama4", llama))
                             if args.design in ("both", name)}
     first = next(iter(out[sizes[0][0]].values()))
     key = f"decode_b{args.batch if args.only_decode else 8}"
-    line = base_line("decode tok/s at batch 8, context 2,048 (Sezazen design, first size)", first.get(key + "_tok_s", 0.0), "tok/s",
+    line = base_line(f"decode tok/s at batch 8, context 2,048 ({design.capitalize()} design, first size)", first.get(key + "_tok_s", 0.0), "tok/s",
                      steps, warmup, first.get(key + "_ms", 0.0),
-                     {"model": "sezazen beside llama4 at equal layer sizes", "layer_runs": 8, "prefill_tokens": T, "context": C,
+                     {"model": f"{design} beside llama4 at equal layer sizes", "layer_runs": 8, "prefill_tokens": T, "context": C,
                       "sizes": {s[0]: dict(zip(("width", "q_heads", "kv_heads", "key_dim", "value_dim", "experts", "top", "expert_ff",
                                                 "shared_ff", "dense_ff", "vocab"), s[1:])) for s in DESIGN_SIZES},
                       "global_batch": 8, "seq_len": C, "page_size": 64, "parallelism": "single-gpu",
@@ -636,8 +678,8 @@ def main(argv=None):
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--config", choices=["scout", "maverick", "long", "sezazen"], default="scout",
-                    help="scout: the benchmark line; maverick, long, sezazen: further workloads, one line each")
+    ap.add_argument("--config", choices=["scout", "maverick", "long", "sezazen", "mibezen"], default="scout",
+                    help="scout: the benchmark line; maverick, long, sezazen, mibezen: further workloads, one line each")
     ap.add_argument("--layers", type=int, default=FULL_LAYERS)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=8192)
@@ -647,7 +689,8 @@ def main(argv=None):
     ap.add_argument("--only-prefill", action="store_true", help="measure the prefill step only (for profiling)")
     ap.add_argument("--verbose", action="store_true", help="print the single prefill timings to standard error")
     ap.add_argument("--size", default=None, help="--config sezazen: only this set of layer sizes (small, medium, ...)")
-    ap.add_argument("--design", choices=["both", "sezazen", "llama4"], default="both", help="--config sezazen: only this design")
+    ap.add_argument("--design", choices=["both", "sezazen", "mibezen", "llama4"], default="both",
+                    help="--config sezazen / mibezen: only this design")
     args = ap.parse_args(argv)
     if args.impl == "reference":
         return run_reference(args)
@@ -660,7 +703,7 @@ def main(argv=None):
     if args.config == "long":
         run_long(args)
         return 0
-    if args.config == "sezazen":
+    if args.config in ("sezazen", "mibezen"):
         run_sezazen(args)
         return 0
     if args.warmup < 3:

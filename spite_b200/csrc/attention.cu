@@ -250,9 +250,15 @@ int check_common(const StepTokens* b, const PagedCache* c, int num_heads, int ma
 
 }  // namespace
 
-SPITE_API int spite_qk_prepare(int dtype, const QkPrepareParams* p, const StepTokens* b,
+SPITE_API int spite_qk_prepare(int dtype, const QkPrepareParams* given, const StepTokens* b,
                                const PagedCache* c, void* stream) {
-    if (!p || !p->qkv || !p->q_out) return SPITE_BAD_ARG;
+    if (!given || !given->qkv || !given->q_out) return SPITE_BAD_ARG;
+    if (!c) return SPITE_BAD_ARG;
+    QkPrepareParams filled = *given;                          // a caller that leaves the later fields at zero means: rows
+    if (filled.qkv_stride == 0)                               // without anything behind the heads, a pure rotation
+        filled.qkv_stride = (long long)(filled.num_heads + 2 * c->num_kv_heads) * c->head_dim;
+    if (filled.rot_amplitude == 0.f) filled.rot_amplitude = 1.f;
+    const QkPrepareParams* p = &filled;
     const int chk = check_common(b, c, p->num_heads);
     if (chk != SPITE_OK) return chk;
     if (b->n_tokens == 0) return SPITE_OK;

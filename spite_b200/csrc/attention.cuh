@@ -46,8 +46,8 @@ struct QkPrepareParams {
     float temperature_scale;
     int num_heads;
     int write_cache;            // append k and v to the cache
-    long long qkv_stride;       // elements between two tokens' rows of qkv (>= (nq + 2 nkv) * head_dim)
-    float rot_amplitude;        // cos and sin of the rotation are multiplied by this (1: a pure rotation)
+    long long qkv_stride;       // elements between two tokens' rows of qkv (>= (nq + 2 nkv) * head_dim; 0: exactly that)
+    float rot_amplitude;        // cos and sin of the rotation are multiplied by this (1, or 0 for unset: a pure rotation)
     // value blending: element i < v_mix_dim of kv head g's value becomes (1 - v_mix) v + v_mix * v_other[t * v_other_stride +
     // g * v_other_head + i] before it is cached (v_other null: no blending)
     const void* v_other;

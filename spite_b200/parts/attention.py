@@ -45,8 +45,8 @@ class PagedAttention(Mixer):
         super().__init__(ctx)
         if num_heads % num_kv_heads:
             raise ConfigError(f"{num_heads} query heads cannot share {num_kv_heads} kv heads evenly")
-        if head_dim % 2 or head_dim > 256:
-            raise ConfigError(f"head_dim {head_dim} must be even and at most 256")
+        if head_dim < 1 or head_dim > 256:
+            raise ConfigError(f"head_dim {head_dim} must lie in 1..256")
         self.d, self.nq, self.nkv = int(hidden_size), int(num_heads), int(num_kv_heads)
         self.kd = int(head_dim)
         self.vd = int(value_dim) if value_dim else self.kd
@@ -74,6 +74,8 @@ class PagedAttention(Mixer):
         # A rotation or a per-head norm would have to know which elements of a row are padding: a layer
         # with either keeps its rows as they are.
         may_pad = qk_norm_eps is None and self.position.rotation() is None
+        if self.kd % 2 and not may_pad:
+            raise ConfigError(f"head_dim {head_dim} must be even where heads rotate or are normed")
         hd = max(self.kd, self.vd)
         step = 16 if self.vd != self.kd and ctx.dtype == torch.bfloat16 and hd <= 128 else 2
         self.hd = -(-hd // step) * step

@@ -295,8 +295,49 @@ def test_attention_refuses_sizes_outside_its_domain(libs):
     k = attention_case(hd=64, nq=34, nkv=2)                            # 17 query heads on a kv head
     for name in ("attention_mma", "attention_rows", "attention_decode"):
         assert calls[name](k) == UNSUPPORTED and untouched(k["out"]), name
-    k = attention_case(hd=258)                                         # beyond the general kernel's 256
+    k = attention_case(hd=642)                                         # beyond the general kernel's 640
     assert calls["attention"](k) == UNSUPPORTED and untouched(k["out"])
+    k = attention_case(hd=258)                                         # the prepare kernel takes heads of up to 256
+    assert libs["attention"].spite_qk_prepare(1, C.byref(k["qp"]), C.byref(k["b"]), C.byref(k["c"]), None) == UNSUPPORTED
+
+
+def test_latent_entry_points(libs):
+    from spite_b200.kernels.cuda import LatentPrepareParams, LatentQueryParams
+    lib = libs["latent"]
+    M, rq, rkv, rot, nq, dn, row = 3, 8, 10, 4, 2, 6, 16
+    k = attention_case(hd=row, nq=nq, nkv=1, page=16, M=M)
+    down = torch.ones((M, rq + rkv + rot + nq), dtype=torch.float32, device=DEV)
+    cq, gates = canary((M, rq), torch.bfloat16), canary((M, nq))
+    gq, gk, fr = (torch.ones(n, dtype=torch.float32, device=DEV) for n in (rq, rkv, rot // 2))
+
+    def prep(**kw):
+        a = dict(down=down.data_ptr(), down_stride=down.shape[1], cq_out=cq.data_ptr(), q_gain=gq.data_ptr(), kv_gain=gk.data_ptr(),
+                 inv_freq=fr.data_ptr(), rot_amplitude=1.0, eps=1e-5, q_rank=rq, kv_rank=rkv, rot_dim=rot, num_gates=nq,
+                 gates_out=gates.data_ptr(), write_cache=1)
+        a.update(kw)
+        return lib.spite_latent_prepare(1, C.byref(LatentPrepareParams(**a)), C.byref(k["b"]), C.byref(k["c"]), None)
+    for kw in (dict(down=None), dict(cq_out=None), dict(q_gain=None), dict(inv_freq=None), dict(q_rank=0), dict(rot_dim=3),
+               dict(down_stride=rq + rkv + rot), dict(kv_rank=row)):
+        assert prep(**kw) == BAD_ARG, kw
+        assert untouched(cq, gates) and float(k["kv"].float().abs().sum()) == 0.0
+    assert lib.spite_latent_prepare(9, C.byref(LatentPrepareParams()), C.byref(k["b"]), C.byref(k["c"]), None) == BAD_ARG
+
+    q = torch.ones((M, nq * (dn + rot)), dtype=torch.bfloat16, device=DEV)
+    qa = canary((M, nq * row), torch.bfloat16)
+    rows, offs = canary((nq * M,), torch.int32), canary((nq + 1,), torch.int32)
+    pos = torch.arange(M, dtype=torch.int32, device=DEV)
+
+    def queries(**kw):
+        a = dict(q=q.data_ptr(), q_out=qa.data_ptr(), inv_freq=fr.data_ptr(), rot_amplitude=1.0, num_heads=nq, head_dim=dn,
+                 rot_dim=rot, kv_rank=rkv, row=row, positions=pos.data_ptr(), n_tokens=M, rows_out=rows.data_ptr(),
+                 offsets_out=offs.data_ptr())
+        a.update(kw)
+        return lib.spite_latent_queries(1, C.byref(LatentQueryParams(**a)), None)
+    for kw in (dict(q=None), dict(q_out=None), dict(positions=None), dict(rows_out=None), dict(num_heads=0), dict(rot_dim=5),
+               dict(row=rkv + rot - 1), dict(n_tokens=-1)):
+        assert queries(**kw) == BAD_ARG, kw
+        assert untouched(qa, rows, offs)
+    assert queries(rot_dim=10000, row=10100) == UNSUPPORTED and untouched(qa, rows, offs)
 
 
 def test_prepare_refuses_malformed_calls(libs):

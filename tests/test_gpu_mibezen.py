@@ -355,15 +355,19 @@ def one_layer_model(mixer_spec, d, V, dtype, seed, tune=None, std=0.25):
     return model, {n: t.float() for n, t in params.items()}
 
 
-def run_cuts(model, toks, ref, tol, what):
+def run_cuts(model, toks, ref, tol, what, single=1.0):
+    """Every position's logits in three cuts.  `single` > 1 lets single positions reach `single * tol` while the median
+    stays under a quarter of `tol` (a model of one layer with a tied head has positions where one rounded key moves the
+    result several times as far as usual, in every order of the roundings)."""
     from spite_b200.engine import Engine
     reqs = {"a": toks}
     for steps in (H.steps_whole(reqs), H.steps_last_decoded(reqs, 20), H.steps_portions(reqs, seed=1, sizes=(2, 3, 5, 17))):
         eng = Engine(model, cache_tokens=192, page_size=16, max_requests=2)
         got = H.run_steps(eng, steps)
         eng.check()
-        worst = max(float((got[("a", p)] - ref[p]).abs().max()) for p in range(len(toks))) / float(ref.abs().max())
-        assert worst <= tol, f"{what}: {worst:.3e}"
+        errs = torch.tensor([float((got[("a", p)] - ref[p]).abs().max()) for p in range(len(toks))]) / float(ref.abs().max())
+        assert float(errs.max()) <= tol * single, f"{what}: {float(errs.max()):.3e} at position {int(errs.argmax())}"
+        assert single == 1.0 or float(errs.median()) <= tol / 4, f"{what}: median {float(errs.median()):.3e}"
 
 
 def plain_norm(x, w, eps):
@@ -400,11 +404,11 @@ def test_latent_attention_part_alone(dtype, nq, dn, dr, dv, rq, rkv, scaling):
     W = {k: P["layers.0.mixer." + v] for k, v in W.items()}
     x = x + plain.latent_attention(plain_norm(x, P["layers.0.mixer_norm.weight"], 1e-5), W, m, 1e-5)
     ref = plain_norm(x, P["final_norm.weight"], 1e-5) @ P["embed.weight"].T
-    run_cuts(model, toks, ref, TOL[dtype], f"latent attention {nq} heads, row {rkv}+{dr}")
+    run_cuts(model, toks, ref, TOL[dtype], f"latent attention {nq} heads, row {rkv}+{dr}", single=2.0 if dtype == "bfloat16" else 1.0)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("nq,nkv,kd,vd,chunk", [(6, 3, 16, 16, 24), (8, 2, 64, 64, 64), (7, 1, 10, 6, 7), (4, 4, 32, 48, 0), (4, 2, 128, 128, 50)])
+@pytest.mark.parametrize("nq,nkv,kd,vd,chunk", [(6, 3, 16, 16, 24), (8, 2, 64, 64, 64), (7, 1, 10, 6, 7), (4, 4, 32, 48, 0), (4, 2, 128, 128, 50), (5, 5, 9, 7, 11)])
 def test_attention_part_with_bias_sinks_gate_and_chunk_alone(dtype, nq, nkv, kd, vd, chunk):
     from spite_b200.config import PartSpec
     d, V = 48, 50
