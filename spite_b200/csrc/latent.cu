@@ -7,7 +7,8 @@
 //    becomes [normed key/value latent ; rotated shared part ; zeros].  The gates become sigmoid(column).
 //  * latent_queries: the rotating tail of every query head is rotated the same way into the row that the
 //    attention kernels read ([kv_rank elements left for the product with the heads' key matrices ; rotated
-//    tail ; zeros]), and the (token, head) rows are listed head by head for the products per head.
+//    tail ; zeros]), the (token, head) rows are listed head by head for the products per head, and the unrotated
+//    parts are laid out in that order, so that the product that follows reads its rows in place.
 //
 // One block a token; float32 arithmetic whatever the element type.
 #include "attention.cuh"
@@ -37,6 +38,8 @@ struct LatentQueryParams {
     int n_tokens;
     int* rows_out;              // [num_heads * tokens]: rows_out[h * tokens + t] = t * num_heads + h
     int* offsets_out;           // [num_heads + 1]: offsets_out[h] = h * tokens
+    void* q_sorted_out;         // [num_heads * tokens, head_dim] or null: the unrotated parts head by head (row h * tokens + t),
+                                // the order in which the product with the heads' key matrices takes its rows
 };
 
 namespace {
@@ -111,6 +114,13 @@ __global__ void __launch_bounds__(128) latent_queries_kernel(const LatentQueryPa
         const float cs = cs_sn[i], sn = cs_sn[half + i];
         out[h * p.row + p.kv_rank + 2 * i] = from_f32<T>(a * cs - bb * sn);
         out[h * p.row + p.kv_rank + 2 * i + 1] = from_f32<T>(bb * cs + a * sn);
+    }
+    if (p.q_sorted_out) {
+        T* sorted = (T*)p.q_sorted_out;
+        for (int e = threadIdx.x; e < p.num_heads * p.head_dim; e += blockDim.x) {
+            const int h = e / p.head_dim, i = e % p.head_dim;
+            sorted[((size_t)h * p.n_tokens + t) * p.head_dim + i] = q[h * qh + i];
+        }
     }
     const int pad = p.row - p.kv_rank - p.rot_dim;
     for (int e = threadIdx.x; e < p.num_heads * pad; e += blockDim.x)

@@ -96,10 +96,11 @@ class KernelSet:
         `row_scale` [M] float32 by place i in the sorted order (s_i = 1 without it)."""
         raise NotImplementedError
 
-    def grouped_linear_rows(self, a, w, rows, offsets, out):
+    def grouped_linear_rows(self, a, w, rows, offsets, out, *, a_sorted=False):
         """out[rows[i], :N] (T) = a[rows[i], :K] @ w[g]^T for every place i of group g's range of `offsets`;
         a [R, lda >= K], w [G, N, K], out [R, ldc >= N].  Rows of `a` and `out` that no place names, and columns
-        beyond K and N, are neither read nor written (a product per head: the rows are (token, head) pairs)."""
+        beyond K and N, are neither read nor written (a product per head: the rows are (token, head) pairs).
+        With `a_sorted`, `a` lies in the list's order already: place i reads a[i, :K]."""
         raise NotImplementedError
 
     # ---- cache
@@ -145,11 +146,13 @@ class KernelSet:
         zeros up to the row's size]; gates_out [M, num_gates] float32 = sigmoid of the gate columns."""
         raise NotImplementedError
 
-    def latent_queries(self, q, q_out, batch, *, num_heads, head_dim, kv_rank, rotation, rows_out, offsets_out):
+    def latent_queries(self, q, q_out, batch, *, num_heads, head_dim, kv_rank, rotation, rows_out, offsets_out,
+                       sorted_out=None):
         """q [M, nq (head_dim + rot)] (T): every head's last `rot` elements are rotated (as in `latent_prepare`) into
         q_out[m, h, kv_rank : kv_rank + rot], and q_out's elements behind them become zero (q_out [M, nq, row] T; its
         first kv_rank elements are left for the product that follows).  Also lists the (token, head) rows head by
-        head: rows_out[h M + m] = m nq + h, offsets_out[h] = h M (int32 [nq M] and [nq + 1])."""
+        head: rows_out[h M + m] = m nq + h, offsets_out[h] = h M (int32 [nq M] and [nq + 1]); `sorted_out` [nq M, head_dim]
+        (T), if given, receives the heads' unrotated parts in that order: sorted_out[h M + m] = q[m, h, :head_dim]."""
         raise NotImplementedError
 
     # ---- mixture of experts

@@ -72,7 +72,7 @@ class LatentQueryParams(C.Structure):
     _fields_ = [("q", C.c_void_p), ("q_out", C.c_void_p), ("inv_freq", C.c_void_p), ("rot_amplitude", C.c_float),
                 ("num_heads", C.c_int), ("head_dim", C.c_int), ("rot_dim", C.c_int), ("kv_rank", C.c_int),
                 ("row", C.c_int), ("positions", C.c_void_p), ("n_tokens", C.c_int),
-                ("rows_out", C.c_void_p), ("offsets_out", C.c_void_p)]
+                ("rows_out", C.c_void_p), ("offsets_out", C.c_void_p), ("q_sorted_out", C.c_void_p)]
 
 
 class AttnMmaExtra(C.Structure):
@@ -589,19 +589,21 @@ class CudaKernels(KernelSet):
                        epilogue=EPI_ADD_F32, scale_by_a_row=0)
         self._gemm(p, "grouped_linear_accumulate", M)
 
-    def grouped_linear_rows(self, a, w, rows, offsets, out):
+    def grouped_linear_rows(self, a, w, rows, offsets, out, *, a_sorted=False):
         self._t(a, self.dtype, "a"); self._t(w, self.dtype, "w"); self._t(out, self.dtype, "out")
         self._t(rows, torch.int32, "rows"); self._t(offsets, torch.int32, "offsets")
         R, lda = a.shape
         G, N, K = w.shape
-        if K > lda or out.shape[0] != R or N > out.shape[1] or offsets.numel() != G + 1 or rows.numel() > R:
-            raise KernelError("grouped_linear_rows: shapes do not fit")
         M = rows.numel()
-        # the rows are gathered and scattered by the same list; columns beyond K of `a` and beyond N of `out` stay out
-        p = GemmParams(A=a.data_ptr(), W=w.data_ptr(), C=out.data_ptr(), a_rows=rows.data_ptr(), c_rows=rows.data_ptr(),
-                       group_offsets=offsets.data_ptr(), row_scale=None, lda=lda, ldc=out.shape[1],
+        if K > lda or (a.shape[0] != M if a_sorted else out.shape[0] != R) or N > out.shape[1] or offsets.numel() != G + 1 \
+                or M > out.shape[0]:
+            raise KernelError("grouped_linear_rows: shapes do not fit")
+        # the rows are gathered and scattered by the same list (or only scattered, if `a` lies in the list's order already);
+        # columns beyond K of `a` and beyond N of `out` stay out
+        p = GemmParams(A=a.data_ptr(), W=w.data_ptr(), C=out.data_ptr(), a_rows=None if a_sorted else rows.data_ptr(),
+                       c_rows=rows.data_ptr(), group_offsets=offsets.data_ptr(), row_scale=None, lda=lda, ldc=out.shape[1],
                        w_group_stride=N * K, n_groups=G, M=M, N=N, K=K, epilogue=EPI_STORE, scale_by_a_row=0)
-        self._gemm(p, "grouped_linear_rows", M, gather_src=a)
+        self._gemm(p, "grouped_linear_rows", M, gather_src=None if a_sorted else a)
 
     # ------------------------------------------------------------------ attention
     def _step_tokens(self, batch, group):
@@ -815,8 +817,11 @@ class CudaKernels(KernelSet):
         self._count("latent", 1)
         _check(st, "latent_prepare")
 
-    def latent_queries(self, q, q_out, batch, *, num_heads, head_dim, kv_rank, rotation, rows_out, offsets_out):
+    def latent_queries(self, q, q_out, batch, *, num_heads, head_dim, kv_rank, rotation, rows_out, offsets_out,
+                       sorted_out=None):
         self._t(q, self.dtype, "q"); self._t(q_out, self.dtype, "q_out")
+        if sorted_out is not None and tuple(self._t(sorted_out, self.dtype, "sorted_out").shape) != (num_heads * q.shape[0], head_dim):
+            raise KernelError("latent_queries: sorted_out must be [heads * tokens, head_dim]")
         self._t(rows_out, torch.int32, "rows_out"); self._t(offsets_out, torch.int32, "offsets_out")
         inv_freq = self._t(rotation.inv_freq, torch.float32, "inv_freq")
         M, rot = q.shape[0], 2 * inv_freq.numel()
@@ -827,7 +832,7 @@ class CudaKernels(KernelSet):
                               rot_amplitude=float(rotation.amplitude), num_heads=int(num_heads), head_dim=int(head_dim),
                               rot_dim=rot, kv_rank=int(kv_rank), row=q_out.shape[1] // num_heads,
                               positions=batch.positions.data_ptr(), n_tokens=M, rows_out=rows_out.data_ptr(),
-                              offsets_out=offsets_out.data_ptr())
+                              offsets_out=offsets_out.data_ptr(), q_sorted_out=_ptr(sorted_out))
         st = self._lib("latent").spite_latent_queries(self._dt, C.byref(p), self._stream())
         self._count("latent", 1)
         _check(st, "latent_queries")

@@ -19,8 +19,8 @@ sigmoid(w_h . x); it is applied to the attention's result before W_uv,h, which i
 
 Steps of `forward`: one product for W_dq, W_dkv and the gates' rows (float32 sums kept); `latent_prepare` (both
 norms in float32, the rotation of k_r, the cache row, the gates); W_uq; `latent_queries` (rotation of q_r into
-the query rows) and the product per head with W_uk^T; attention; the product per head with W_uv; W_o into the
-residual stream.
+the query rows, the unrotated parts laid out head by head) and the product per head with W_uk^T; attention; the
+product per head with W_uv; W_o into the residual stream.
 """
 from __future__ import annotations
 
@@ -120,10 +120,11 @@ class LatentAttention(Mixer):
         qa = torch.empty((M, nq * row), dtype=x.dtype, device=dev)
         rows = torch.empty((nq * M,), dtype=torch.int32, device=dev)
         offsets = torch.empty((nq + 1,), dtype=torch.int32, device=dev)
+        qn = torch.empty((nq * M, self.dn), dtype=x.dtype, device=dev)      # the unrotated parts, head by head
         k.latent_queries(q, qa, batch, num_heads=nq, head_dim=self.dn, kv_rank=self.rkv, rotation=rotation,
-                         rows_out=rows, offsets_out=offsets)
+                         rows_out=rows, offsets_out=offsets, sorted_out=qn)
         # q_n,h -> W_uk,h^T q_n,h, written in front of the rotated part of the same (token, head) row
-        k.grouped_linear_rows(q.view(M * nq, self.dn + self.dr), self.w_uk_t, rows, offsets, qa.view(M * nq, row))
+        k.grouped_linear_rows(qn, self.w_uk_t, rows, offsets, qa.view(M * nq, row), a_sorted=True)
         ol = torch.empty_like(qa)
         more = {"head_gates": gates} if gates is not None else {}
         k.paged_attention(qa, ol, batch, cache, num_heads=nq, window=Window("full", 0),

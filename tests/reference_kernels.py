@@ -119,14 +119,15 @@ class TorchReferenceKernels(KernelSet):
                 y = y * row_scale[lo:hi].to(self.acc)[:, None]
             h[rows[lo:hi]] += y.to(h.dtype)
 
-    def grouped_linear_rows(self, a, w, rows, offsets, out):
+    def grouped_linear_rows(self, a, w, rows, offsets, out, *, a_sorted=False):
         G, N, K = w.shape
         off = offsets.tolist()
         idx = rows.long()
         for g in range(G):
             r = idx[off[g]:off[g + 1]]
             if r.numel():
-                out[r, :N] = self._mm(a[r, :K], w[g]).to(out.dtype)
+                src = a[off[g]:off[g + 1], :K] if a_sorted else a[r, :K]
+                out[r, :N] = self._mm(src, w[g]).to(out.dtype)
 
     # ---- attention
     def qk_prepare(self, qkv, q_out, batch, cache, *, num_heads, rotation, qk_norm, temperature,
@@ -227,7 +228,8 @@ class TorchReferenceKernels(KernelSet):
                 kv[0, page, 0, p % P, :kv_rank] = c[t].to(kv.dtype)
                 kv[0, page, 0, p % P, kv_rank:kv_rank + rot] = kr[t].to(kv.dtype)
 
-    def latent_queries(self, q, q_out, batch, *, num_heads, head_dim, kv_rank, rotation, rows_out, offsets_out):
+    def latent_queries(self, q, q_out, batch, *, num_heads, head_dim, kv_rank, rotation, rows_out, offsets_out,
+                       sorted_out=None):
         M = q.shape[0]
         rot = rotation.inv_freq.numel() * 2
         qv = q.to(self.acc).view(M, num_heads, head_dim + rot)
@@ -238,6 +240,8 @@ class TorchReferenceKernels(KernelSet):
         for h in range(num_heads):
             rows_out[h * M:(h + 1) * M] = m * num_heads + h
         offsets_out.copy_(torch.arange(num_heads + 1, dtype=torch.int32, device=q.device) * M)
+        if sorted_out is not None:
+            sorted_out.copy_(q.view(M, num_heads, head_dim + rot)[:, :, :head_dim].transpose(0, 1).reshape(num_heads * M, head_dim))
 
     def paged_attention(self, q, out, batch, cache, *, num_heads, window, softmax_scale, cache_settled=False,
                         sink_logit=None, head_sinks=None, head_slopes=None, head_gates=None):

@@ -244,8 +244,11 @@ def test_latent_prepare_and_queries(dtype, nq, dn, dr, rq, rkv, row):
     qa = torch.full((M, nq * row), 5.0, dtype=dtype, device=DEV)
     rows = torch.empty(nq * M, dtype=torch.int32, device=DEV)
     offs = torch.empty(nq + 1, dtype=torch.int32, device=DEV)
-    ks.latent_queries(q.to(DEV), qa, batch, num_heads=nq, head_dim=dn, kv_rank=rkv, rotation=rot, rows_out=rows, offsets_out=offs)
+    qs = torch.empty((nq * M, dn), dtype=dtype, device=DEV)
+    ks.latent_queries(q.to(DEV), qa, batch, num_heads=nq, head_dim=dn, kv_rank=rkv, rotation=rot, rows_out=rows, offsets_out=offs,
+                      sorted_out=qs)
     torch.cuda.synchronize()
+    assert torch.equal(qs.cpu().view(nq, M, dn), q.view(M, nq, dn + dr)[:, :, :dn].transpose(0, 1))
     tol = 1e-5 if dtype == torch.float32 else 1.2e-2
     d64 = down.double()
 
@@ -300,6 +303,12 @@ def test_products_per_head(dtype, M, G, K, N, lda, ldc):
     close(out.view(M, G, ldc)[:, :, :N], ref, KTOL[dtype], "product per head")
     if ldc > N:
         assert float((out.view(M, G, ldc)[:, :, N:].float() - 3.0).abs().max()) == 0.0
+    # the same with the rows of `a` laid out head by head already
+    out2 = torch.full((M * G, ldc), 3.0, dtype=dtype, device=DEV)
+    a_sorted = a.view(M, G, lda).transpose(0, 1).reshape(G * M, lda).contiguous()
+    ks.grouped_linear_rows(a_sorted.to(DEV), w.to(DEV), rows, offs, out2, a_sorted=True)
+    torch.cuda.synchronize()
+    close(out2.view(M, G, ldc)[:, :, :N], ref, KTOL[dtype], "product per head, rows in place")
 
 
 # ---------------------------------------------------------------------------- router and experts
