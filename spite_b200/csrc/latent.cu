@@ -44,53 +44,128 @@ struct LatentQueryParams {
 
 namespace {
 
-template <typename T>
+// Two sums over a block of 256 threads at once; every thread receives both.  The order of the additions is a
+// function of the block size only.
+__device__ __forceinline__ void block_sum2(float& a, float& b, float (*scratch)[33]) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    a = warp_sum(a); b = warp_sum(b);
+    if (lane == 0) { scratch[0][warp] = a; scratch[1][warp] = b; }
+    __syncthreads();
+    if (warp == 0) {
+        float x = lane < nwarps ? scratch[0][lane] : 0.f, y = lane < nwarps ? scratch[1][lane] : 0.f;
+        x = warp_sum(x); y = warp_sum(y);
+        if (lane == 0) { scratch[0][32] = x; scratch[1][32] = y; }
+    }
+    __syncthreads();
+    a = scratch[0][32]; b = scratch[1][32];
+}
+
+__device__ __forceinline__ void store4(float* p, float a, float b, float c, float d) { *(float4*)p = make_float4(a, b, c, d); }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, float a, float b, float c, float d) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    *(uint2*)p = make_uint2(*(const unsigned*)&lo, *(const unsigned*)&hi);
+}
+
+// grid tokens, block 128 or 256.  VEC: both ranks and the row stride are multiples of four, q_rank <= 16 * threads and
+// kv_rank <= 4 * threads: a thread keeps its elements of both latents in registers between the sums and the scaling
+// (16-byte loads, one round of block-wide sums for both norms), and everything else the block reads (its page, its
+// gate column, its pair of the shared key part) is asked for before the sums; otherwise the row is walked element by
+// element, twice.
+template <typename T, bool VEC>
 __global__ void __launch_bounds__(256) latent_prepare_kernel(const LatentPrepareParams p, const StepTokens b,
                                                              const PagedCache c) {
-    __shared__ float scratch[33];
+    __shared__ float scratch[2][33];
     pdl_wait();
     pdl_launch_dependents();
     const int t = blockIdx.x;
     const float* in = p.down + (size_t)t * p.down_stride;
+    const float* kv = in + p.q_rank;
     const int pos = b.positions[t];
+    constexpr int QV = 4;                                     // 16-byte groups of the query latent a thread holds
+    float4 qv[QV], kvv = make_float4(0.f, 0.f, 0.f, 0.f);
+    float sq = 0.f, sk = 0.f;
+    // asked for before the sums, used after them (thread i: gate column i, pair i of the shared key part)
+    int page = -1;
+    if (p.write_cache) page = b.block_table[(size_t)b.seg_of_token[t] * b.table_width + pos / c.page_size];
+    const float* kr = kv + p.kv_rank;
+    const int first_gate = p.q_rank + p.kv_rank + p.rot_dim;
+    float gate_in = 0.f, kr0 = 0.f, kr1 = 0.f;
+    if (p.gates_out && (int)threadIdx.x < p.num_gates) gate_in = in[first_gate + threadIdx.x];
+    if (2 * (int)threadIdx.x < p.rot_dim) { kr0 = kr[2 * threadIdx.x]; kr1 = kr[2 * threadIdx.x + 1]; }
+    if (VEC) {
+#pragma unroll
+        for (int r = 0; r < QV; ++r) {
+            const int i = 4 * (threadIdx.x + blockDim.x * r);
+            qv[r] = i < p.q_rank ? *(const float4*)(in + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+            sq += qv[r].x * qv[r].x + qv[r].y * qv[r].y + qv[r].z * qv[r].z + qv[r].w * qv[r].w;
+        }
+        if (4 * threadIdx.x < p.kv_rank) kvv = *(const float4*)(kv + 4 * threadIdx.x);
+        sk = kvv.x * kvv.x + kvv.y * kvv.y + kvv.z * kvv.z + kvv.w * kvv.w;
+    } else {
+        for (int i = threadIdx.x; i < p.q_rank; i += blockDim.x) { const float v = in[i]; sq = fmaf(v, v, sq); }
+        for (int i = threadIdx.x; i < p.kv_rank; i += blockDim.x) { const float v = kv[i]; sk = fmaf(v, v, sk); }
+    }
+    block_sum2(sq, sk, scratch);
 
     // query latent
-    float ss = 0.f;
-    for (int i = threadIdx.x; i < p.q_rank; i += blockDim.x) { const float v = in[i]; ss = fmaf(v, v, ss); }
-    ss = block_sum(ss, scratch);
-    float mul = 1.0f / sqrtf(ss / (float)p.q_rank + p.eps);
+    const float mul_q = 1.0f / sqrtf(sq / (float)p.q_rank + p.eps);
     T* cq = (T*)p.cq_out + (size_t)t * p.q_rank;
-    for (int i = threadIdx.x; i < p.q_rank; i += blockDim.x) cq[i] = from_f32<T>(in[i] * mul * p.q_gain[i]);
+    if (VEC) {
+#pragma unroll
+        for (int r = 0; r < QV; ++r) {
+            const int i = 4 * (threadIdx.x + blockDim.x * r);
+            if (i < p.q_rank) {
+                const float4 g = *(const float4*)(p.q_gain + i);
+                store4(cq + i, qv[r].x * mul_q * g.x, qv[r].y * mul_q * g.y, qv[r].z * mul_q * g.z, qv[r].w * mul_q * g.w);
+            }
+        }
+    } else {
+        for (int i = threadIdx.x; i < p.q_rank; i += blockDim.x) cq[i] = from_f32<T>(in[i] * mul_q * p.q_gain[i]);
+    }
 
     // gates
     if (p.gates_out)
         for (int h = threadIdx.x; h < p.num_gates; h += blockDim.x)
-            p.gates_out[(size_t)t * p.num_gates + h] = 1.0f / (1.0f + expf(-in[p.q_rank + p.kv_rank + p.rot_dim + h]));
+            p.gates_out[(size_t)t * p.num_gates + h] = 1.0f / (1.0f + expf(-(h < (int)blockDim.x ? gate_in : in[first_gate + h])));
 
     // key/value latent and the shared key part: the cache row of this position
-    const float* kv = in + p.q_rank;
-    ss = 0.f;
-    for (int i = threadIdx.x; i < p.kv_rank; i += blockDim.x) { const float v = kv[i]; ss = fmaf(v, v, ss); }
-    ss = block_sum(ss, scratch);
     if (!p.write_cache) return;
-    const int page = b.block_table[(size_t)b.seg_of_token[t] * b.table_width + pos / c.page_size];
     if (page < 0 || page >= c.n_pages) return;               // the host never lets this happen
-    mul = 1.0f / sqrtf(ss / (float)p.kv_rank + p.eps);
+    const float mul_k = 1.0f / sqrtf(sk / (float)p.kv_rank + p.eps);
     T* row = (T*)c.kv + ((size_t)page * c.page_size + pos % c.page_size) * c.head_dim;
-    for (int i = threadIdx.x; i < p.kv_rank; i += blockDim.x) row[i] = from_f32<T>(kv[i] * mul * p.kv_gain[i]);
-    const float* kr = kv + p.kv_rank;
+    if (VEC) {
+        const int i = 4 * threadIdx.x;
+        if (i < p.kv_rank) {
+            row[i] = from_f32<T>(kvv.x * mul_k * p.kv_gain[i]); row[i + 1] = from_f32<T>(kvv.y * mul_k * p.kv_gain[i + 1]);
+            row[i + 2] = from_f32<T>(kvv.z * mul_k * p.kv_gain[i + 2]); row[i + 3] = from_f32<T>(kvv.w * mul_k * p.kv_gain[i + 3]);
+        }
+    } else {
+        for (int i = threadIdx.x; i < p.kv_rank; i += blockDim.x) row[i] = from_f32<T>(kv[i] * mul_k * p.kv_gain[i]);
+    }
     for (int i = threadIdx.x; 2 * i < p.rot_dim; i += blockDim.x) {
         float sn, cs;
         sincosf((float)pos * p.inv_freq[i], &sn, &cs);
         sn *= p.rot_amplitude; cs *= p.rot_amplitude;
-        const float a = kr[2 * i], bb = kr[2 * i + 1];
+        const float a = i < (int)blockDim.x ? kr0 : kr[2 * i], bb = i < (int)blockDim.x ? kr1 : kr[2 * i + 1];
         row[p.kv_rank + 2 * i] = from_f32<T>(a * cs - bb * sn);
         row[p.kv_rank + 2 * i + 1] = from_f32<T>(bb * cs + a * sn);
     }
     for (int i = p.kv_rank + p.rot_dim + threadIdx.x; i < c.head_dim; i += blockDim.x) row[i] = from_f32<T>(0.f);
 }
 
-template <typename T>
+__device__ __forceinline__ void load_pair(const float* p, float& a, float& b) { const float2 v = *(const float2*)p; a = v.x; b = v.y; }
+__device__ __forceinline__ void load_pair(const __nv_bfloat16* p, float& a, float& b) {
+    const __nv_bfloat162 v = *(const __nv_bfloat162*)p;
+    a = __low2float(v); b = __high2float(v);
+}
+__device__ __forceinline__ void store_pair(float* p, float a, float b) { *(float2*)p = make_float2(a, b); }
+__device__ __forceinline__ void store_pair(__nv_bfloat16* p, float a, float b) { *(__nv_bfloat162*)p = __floats2bfloat162_rn(a, b); }
+__device__ __forceinline__ void copy4(float* dst, const float* src) { *(float4*)dst = *(const float4*)src; }
+__device__ __forceinline__ void copy4(__nv_bfloat16* dst, const __nv_bfloat16* src) { *(uint2*)dst = *(const uint2*)src; }
+
+// grid tokens, block 128.  WIDE: head_dim and rot_dim are multiples of four and kv_rank and the row size are even, so a
+// rotating pair moves as one word and the unrotated parts four elements at a time.
+template <typename T, bool WIDE>
 __global__ void __launch_bounds__(128) latent_queries_kernel(const LatentQueryParams p) {
     extern __shared__ float cs_sn[];                         // [rot_dim / 2] cos, then as many sin
     pdl_wait();
@@ -110,16 +185,28 @@ __global__ void __launch_bounds__(128) latent_queries_kernel(const LatentQueryPa
     T* out = (T*)p.q_out + (size_t)t * p.num_heads * p.row;
     for (int e = threadIdx.x; e < p.num_heads * half; e += blockDim.x) {
         const int h = e / half, i = e % half;
-        const float a = to_f32(q[h * qh + p.head_dim + 2 * i]), bb = to_f32(q[h * qh + p.head_dim + 2 * i + 1]);
+        const T* src = q + h * qh + p.head_dim + 2 * i;
+        T* dst = out + h * p.row + p.kv_rank + 2 * i;
+        float a, bb;
+        if (WIDE) load_pair(src, a, bb);
+        else { a = to_f32(src[0]); bb = to_f32(src[1]); }
         const float cs = cs_sn[i], sn = cs_sn[half + i];
-        out[h * p.row + p.kv_rank + 2 * i] = from_f32<T>(a * cs - bb * sn);
-        out[h * p.row + p.kv_rank + 2 * i + 1] = from_f32<T>(bb * cs + a * sn);
+        if (WIDE) store_pair(dst, a * cs - bb * sn, bb * cs + a * sn);
+        else { dst[0] = from_f32<T>(a * cs - bb * sn); dst[1] = from_f32<T>(bb * cs + a * sn); }
     }
     if (p.q_sorted_out) {
         T* sorted = (T*)p.q_sorted_out;
-        for (int e = threadIdx.x; e < p.num_heads * p.head_dim; e += blockDim.x) {
-            const int h = e / p.head_dim, i = e % p.head_dim;
-            sorted[((size_t)h * p.n_tokens + t) * p.head_dim + i] = q[h * qh + i];
+        if (WIDE) {
+            const int quarter = p.head_dim / 4;
+            for (int e = threadIdx.x; e < p.num_heads * quarter; e += blockDim.x) {
+                const int h = e / quarter, i = 4 * (e % quarter);
+                copy4(sorted + ((size_t)h * p.n_tokens + t) * p.head_dim + i, q + h * qh + i);
+            }
+        } else {
+            for (int e = threadIdx.x; e < p.num_heads * p.head_dim; e += blockDim.x) {
+                const int h = e / p.head_dim, i = e % p.head_dim;
+                sorted[((size_t)h * p.n_tokens + t) * p.head_dim + i] = q[h * qh + i];
+            }
         }
     }
     const int pad = p.row - p.kv_rank - p.rot_dim;
@@ -143,9 +230,18 @@ SPITE_API int spite_latent_prepare(int dtype, const LatentPrepareParams* p, cons
     if (c->head_dim < p->kv_rank + p->rot_dim) return SPITE_BAD_ARG;
     if (b->n_tokens == 0) return SPITE_OK;
     cudaStream_t st = (cudaStream_t)stream;
-    if (dtype == SPITE_DT_F32) SPITE_LAUNCH(latent_prepare_kernel<float>, b->n_tokens, 256, 0, st, *p, *b, *c);
-    else if (dtype == SPITE_DT_BF16) SPITE_LAUNCH(latent_prepare_kernel<__nv_bfloat16>, b->n_tokens, 256, 0, st, *p, *b, *c);
-    else return SPITE_BAD_ARG;
+    // 128 threads hold a query latent of up to 2,048 elements: two loads of a thread on their way instead of one, and
+    // twice the blocks a multiprocessor
+    const int threads = (p->q_rank <= 2048 && p->kv_rank <= 512) ? 128 : 256;
+    const bool vec = p->q_rank % 4 == 0 && p->kv_rank % 4 == 0 && p->down_stride % 4 == 0 && p->q_rank <= 16 * threads &&
+                     p->kv_rank <= 4 * threads && (((uintptr_t)p->down | (uintptr_t)p->cq_out | (uintptr_t)p->q_gain) & 15) == 0;
+    if (dtype == SPITE_DT_F32) {
+        if (vec) SPITE_LAUNCH((latent_prepare_kernel<float, true>), b->n_tokens, threads, 0, st, *p, *b, *c);
+        else SPITE_LAUNCH((latent_prepare_kernel<float, false>), b->n_tokens, threads, 0, st, *p, *b, *c);
+    } else if (dtype == SPITE_DT_BF16) {
+        if (vec) SPITE_LAUNCH((latent_prepare_kernel<__nv_bfloat16, true>), b->n_tokens, threads, 0, st, *p, *b, *c);
+        else SPITE_LAUNCH((latent_prepare_kernel<__nv_bfloat16, false>), b->n_tokens, threads, 0, st, *p, *b, *c);
+    } else return SPITE_BAD_ARG;
     return spite_launch_status();
 }
 
@@ -157,8 +253,14 @@ SPITE_API int spite_latent_queries(int dtype, const LatentQueryParams* p, void* 
     if (p->n_tokens == 0) return SPITE_OK;
     cudaStream_t st = (cudaStream_t)stream;
     const size_t smem = (size_t)p->rot_dim * sizeof(float);
-    if (dtype == SPITE_DT_F32) SPITE_LAUNCH(latent_queries_kernel<float>, p->n_tokens, 128, smem, st, *p);
-    else if (dtype == SPITE_DT_BF16) SPITE_LAUNCH(latent_queries_kernel<__nv_bfloat16>, p->n_tokens, 128, smem, st, *p);
-    else return SPITE_BAD_ARG;
+    const bool wide = p->head_dim % 4 == 0 && p->rot_dim % 4 == 0 && p->kv_rank % 2 == 0 && p->row % 2 == 0 &&
+                      (((uintptr_t)p->q | (uintptr_t)p->q_out | (uintptr_t)p->q_sorted_out) & 15) == 0;
+    if (dtype == SPITE_DT_F32) {
+        if (wide) SPITE_LAUNCH((latent_queries_kernel<float, true>), p->n_tokens, 128, smem, st, *p);
+        else SPITE_LAUNCH((latent_queries_kernel<float, false>), p->n_tokens, 128, smem, st, *p);
+    } else if (dtype == SPITE_DT_BF16) {
+        if (wide) SPITE_LAUNCH((latent_queries_kernel<__nv_bfloat16, true>), p->n_tokens, 128, smem, st, *p);
+        else SPITE_LAUNCH((latent_queries_kernel<__nv_bfloat16, false>), p->n_tokens, 128, smem, st, *p);
+    } else return SPITE_BAD_ARG;
     return spite_launch_status();
 }
