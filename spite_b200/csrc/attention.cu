@@ -231,7 +231,7 @@ __global__ void __launch_bounds__(128) paged_attention_kernel(const AttentionPar
         for (int r = 0; r < MAXD; ++r) acc[r] *= corr;
     }
     const float inv = gate_of(p, t, h) / fmaxf(l, 1e-30f);
-    T* out = (T*)p.out + ((size_t)t * nq + h) * hd;
+    T* out = (T*)p.out + out_row_of(p, t, h) * hd;
 #pragma unroll
     for (int r = 0; r < MAXD; ++r) {
         const int d = lane + 32 * r;

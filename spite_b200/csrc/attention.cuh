@@ -71,7 +71,14 @@ struct AttentionParams {
     const float* head_sinks;    // [num_heads] or null: with has_sink, head h's sink has the score head_sinks[h] instead
     const float* head_slopes;   // [num_heads] or null: head_slopes[h] * (query position - key position) is taken off a score
     const float* head_gates;    // [tokens, num_heads] or null: head h's output of token t is multiplied by head_gates[t * nq + h]
+    int out_by_head_tokens;     // 0: out is [tokens, num_heads, head_dim]; n > 0: out is [num_heads, n, head_dim], head by head
+                                // (n the tokens of the step), the order in which a product per head reads its rows
 };
+
+// Where the output row of (token, head) starts, in rows of head_dim elements.
+__device__ __forceinline__ size_t out_row_of(const AttentionParams& p, int token, int head) {
+    return p.out_by_head_tokens > 0 ? (size_t)head * p.out_by_head_tokens + token : (size_t)token * p.num_heads + head;
+}
 
 // The score of head `head`'s sink (only meaningful with has_sink).
 __device__ __forceinline__ float sink_of(const AttentionParams& p, int head) {

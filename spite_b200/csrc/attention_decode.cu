@@ -319,7 +319,7 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const __grid_const
         if (x.n_splits == 1) {
             const int tok = t0 + r / G, head = kvh * G + r % G;
             acc *= fold_sink(p, head, m, l) * gate_of(p, tok, head);
-            ((__nv_bfloat16*)p.out)[((size_t)tok * nq + head) * HD + d] = __float2bfloat16_rn(acc / fmaxf(l, 1e-30f));
+            ((__nv_bfloat16*)p.out)[out_row_of(p, tok, head) * HD + d] = __float2bfloat16_rn(acc / fmaxf(l, 1e-30f));
         } else {
             __stcg(part + r * ROW + d, acc);
             if (d == 0) { __stcg(part + r * ROW + HD, m); __stcg(part + r * ROW + HD + 1, l); }
@@ -405,7 +405,7 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const __grid_const
         const float inv = inv_s[r];
         const int tok = t0 + r / G, head = kvh * G + r % G;
         const unsigned lo = pack_bf16(acc.x * inv, acc.y * inv), hi = pack_bf16(acc.z * inv, acc.w * inv);
-        *(uint2*)((__nv_bfloat16*)p.out + ((size_t)tok * nq + head) * HD + 4 * d4) = make_uint2(lo, hi);
+        *(uint2*)((__nv_bfloat16*)p.out + out_row_of(p, tok, head) * HD + 4 * d4) = make_uint2(lo, hi);
     }
 }
 

@@ -268,7 +268,7 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const AttentionPar
         const int tok = t0 + r / G, head = kvh * G + r % G;
         if (x.n_splits == 1) {
             acc *= fold_sink(p, head, m, l) * gate_of(p, tok, head);
-            ((__nv_bfloat16*)p.out)[((size_t)tok * nq + head) * HD + d] = __float2bfloat16_rn(acc / fmaxf(l, 1e-30f));
+            ((__nv_bfloat16*)p.out)[out_row_of(p, tok, head) * HD + d] = __float2bfloat16_rn(acc / fmaxf(l, 1e-30f));
         } else {
             // partial results are indexed by the block's place among this kernel's blocks, not by the
             // token's place in the step: a long prompt portion beside one decoded token costs no scratch
@@ -325,7 +325,7 @@ __global__ void __launch_bounds__(MERGE_THREADS) attn_merge_kernel(const float* 
     const float shrink = fold_sink(p, head, m, l);          // the sink joins once, after the splits have met
     const float inv = shrink * gate_of(p, tok, head) / fmaxf(l, 1e-30f);
     const float* o = o_part + row * n_splits * hd;
-    __nv_bfloat16* dst = out + ((size_t)tok * num_heads + head) * hd;
+    __nv_bfloat16* dst = out + out_row_of(p, tok, head) * hd;
     for (int d = tid; d < hd; d += MERGE_THREADS) {
         float acc = 0.f;
 #pragma unroll 4

@@ -241,7 +241,7 @@ __global__ void __launch_bounds__(WARPS * 32) attn_rows_kernel(const AttentionPa
         float l = l_run[h];
         const float shrink = fold_sink(p, head, m_run[h], l);
         const float inv = shrink * gate_of(p, tok, head) / fmaxf(l, 1e-30f);
-        __nv_bfloat16* dst = (__nv_bfloat16*)p.out + ((size_t)tok * nq + head) * HD + 2 * cc;
+        __nv_bfloat16* dst = (__nv_bfloat16*)p.out + out_row_of(p, tok, head) * HD + 2 * cc;
 #pragma unroll
         for (int n = 0; n < 2 * NK; ++n)
             *(unsigned*)(dst + 8 * n) = pack_bf16(o[n][2 * h] * inv, o[n][2 * h + 1] * inv);

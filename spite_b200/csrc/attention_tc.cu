@@ -396,7 +396,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                         l = l * shrink + exp2f(sink2 - m2);
                     }
                     const float inv = shrink * gate_of(p, tok, head) / fmaxf(l, 1e-30f);
-                    __nv_bfloat16* dst = (__nv_bfloat16*)p.out + ((size_t)tok * nq + head) * HD;
+                    __nv_bfloat16* dst = (__nv_bfloat16*)p.out + out_row_of(p, tok, head) * HD;
 #pragma unroll 1
                     for (int c0 = 0; c0 < HD; c0 += 32) {
                         float o[32];

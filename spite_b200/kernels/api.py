@@ -124,8 +124,10 @@ class KernelSet:
         raise NotImplementedError
 
     def paged_attention(self, q, out, batch, cache, *, num_heads, window, softmax_scale, cache_settled=False,
-                        sink_logit=None, head_sinks=None, head_slopes=None, head_gates=None):
+                        sink_logit=None, head_sinks=None, head_slopes=None, head_gates=None, out_by_head=False):
         """out[M, nq hd] = softmax(q K^T * scale over the visible cached keys) V.
+        `out_by_head`: the result is laid out head by head instead, out[nq, M, hd] (the order in which a product per
+        head reads its rows).
         `sink_logit`: the softmax's denominator also holds exp(sink_logit), a key without a value;
         `head_sinks` float32 [nq]: the same with a score of its own for every head.
         `head_slopes` float32 [nq]: slope_h * (query position - key position) is taken off head h's scores.

@@ -57,7 +57,8 @@ class AttentionParams(C.Structure):
     _fields_ = [("q", C.c_void_p), ("out", C.c_void_p), ("num_heads", C.c_int),
                 ("window_kind", C.c_int), ("window_size", C.c_int), ("softmax_scale", C.c_float),
                 ("has_sink", C.c_int), ("sink_logit", C.c_float),
-                ("head_sinks", C.c_void_p), ("head_slopes", C.c_void_p), ("head_gates", C.c_void_p)]
+                ("head_sinks", C.c_void_p), ("head_slopes", C.c_void_p), ("head_gates", C.c_void_p),
+                ("out_by_head_tokens", C.c_int)]
 
 
 class LatentPrepareParams(C.Structure):
@@ -664,8 +665,10 @@ class CudaKernels(KernelSet):
 
 
     def paged_attention(self, q, out, batch, cache, *, num_heads, window, softmax_scale, cache_settled=False,
-                        sink_logit=None, head_sinks=None, head_slopes=None, head_gates=None):
+                        sink_logit=None, head_sinks=None, head_slopes=None, head_gates=None, out_by_head=False):
         self._t(q, self.dtype, "q"); self._t(out, self.dtype, "out")
+        if out.numel() != q.numel():
+            raise KernelError("paged_attention: out must have as many elements as q")
         for name, t, n in (("head_sinks", head_sinks, num_heads), ("head_slopes", head_slopes, num_heads),
                            ("head_gates", head_gates, q.shape[0] * num_heads)):
             if t is not None and self._t(t, torch.float32, name).numel() != n:
@@ -677,7 +680,8 @@ class CudaKernels(KernelSet):
                             softmax_scale=float(softmax_scale),
                             has_sink=int(sink_logit is not None or head_sinks is not None),
                             sink_logit=float(sink_logit or 0.0), head_sinks=_ptr(head_sinks),
-                            head_slopes=_ptr(head_slopes), head_gates=_ptr(head_gates))
+                            head_slopes=_ptr(head_slopes), head_gates=_ptr(head_gates),
+                            out_by_head_tokens=q.shape[0] if out_by_head else 0)
         b, c = self._step_tokens(batch, cache.group), self._paged(cache)
         group = num_heads // c.num_kv_heads
         if (self.dtype == torch.bfloat16 and c.head_dim % 16 == 0 and c.head_dim <= 128 and group <= 16

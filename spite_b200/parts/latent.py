@@ -19,8 +19,8 @@ sigmoid(w_h . x); it is applied to the attention's result before W_uv,h, which i
 
 Steps of `forward`: one product for W_dq, W_dkv and the gates' rows (float32 sums kept); `latent_prepare` (both
 norms in float32, the rotation of k_r, the cache row, the gates); W_uq; `latent_queries` (rotation of q_r into
-the query rows, the unrotated parts laid out head by head) and the product per head with W_uk^T; attention; the
-product per head with W_uv; W_o into the residual stream.
+the query rows, the unrotated parts laid out head by head) and the product per head with W_uk^T; attention, its
+result laid out head by head; the product per head with W_uv; W_o into the residual stream.
 """
 from __future__ import annotations
 
@@ -125,10 +125,10 @@ class LatentAttention(Mixer):
                          rows_out=rows, offsets_out=offsets, sorted_out=qn)
         # q_n,h -> W_uk,h^T q_n,h, written in front of the rotated part of the same (token, head) row
         k.grouped_linear_rows(qn, self.w_uk_t, rows, offsets, qa.view(M * nq, row), a_sorted=True)
-        ol = torch.empty_like(qa)
+        ol = torch.empty((nq * M, row), dtype=x.dtype, device=dev)           # head by head, as the next product reads it
         more = {"head_gates": gates} if gates is not None else {}
         k.paged_attention(qa, ol, batch, cache, num_heads=nq, window=Window("full", 0),
-                          softmax_scale=self.softmax_scale, cache_settled=True, **more)
+                          softmax_scale=self.softmax_scale, cache_settled=True, out_by_head=True, **more)
         o = torch.empty((M, nq * self.dv), dtype=x.dtype, device=dev)
-        k.grouped_linear_rows(ol.view(M * nq, row), self.w_uv, rows, offsets, o.view(M * nq, self.dv))
+        k.grouped_linear_rows(ol, self.w_uv, rows, offsets, o.view(M * nq, self.dv), a_sorted=True)
         k.linear(o, self.wo, h, accumulate=True)

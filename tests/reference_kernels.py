@@ -244,7 +244,7 @@ class TorchReferenceKernels(KernelSet):
             sorted_out.copy_(q.view(M, num_heads, head_dim + rot)[:, :, :head_dim].transpose(0, 1).reshape(num_heads * M, head_dim))
 
     def paged_attention(self, q, out, batch, cache, *, num_heads, window, softmax_scale, cache_settled=False,
-                        sink_logit=None, head_sinks=None, head_slopes=None, head_gates=None):
+                        sink_logit=None, head_sinks=None, head_slopes=None, head_gates=None, out_by_head=False):
         kv = cache.kv
         nkv, P, hd = kv.shape[2], kv.shape[3], kv.shape[4]
         nq = num_heads
@@ -274,7 +274,10 @@ class TorchReferenceKernels(KernelSet):
                 o = w @ V[:, h // group, :]
                 if head_gates is not None:
                     o = o * head_gates[t, h].to(self.acc)
-                out[t, h * hd:(h + 1) * hd] = o.to(out.dtype)
+                if out_by_head:
+                    out.view(nq, M, hd)[h, t] = o.to(out.dtype)
+                else:
+                    out[t, h * hd:(h + 1) * hd] = o.to(out.dtype)
 
     # ---- mixture of experts
     def moe_route(self, x, w_router, top_k, want_logits=False, scoring="sigmoid") -> Routing:

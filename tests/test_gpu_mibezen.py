@@ -177,6 +177,12 @@ def test_a_cache_of_one_plane_serves_keys_and_values(case):
     assert ks.launches_by_library[library] > 0, dict(ks.launches_by_library)
     ref = biased_attention_reference(q, k_all, k_all, specs, nq, 1, 0.2, Window("full", 0), None, None, gates)
     close(out.view(M, nq, hd), ref, KTOL[dtype], f"keys as values ({library})")
+    # the same result laid out head by head
+    by_head = torch.empty((nq * M, hd), dtype=dtype, device=DEV)
+    ks.paged_attention(q.reshape(M, nq * hd).to(DEV), by_head, batch, LayerCache(0, two[:1].contiguous().to(DEV), None, P, False),
+                       num_heads=nq, window=Window("full", 0), softmax_scale=0.2, head_gates=gates.to(DEV), out_by_head=True)
+    torch.cuda.synchronize()
+    assert torch.equal(by_head.view(nq, M, hd).transpose(0, 1).contiguous().view(M, nq * hd), out)
 
 
 # ---------------------------------------------------------------------------- the prepare kernel's additions
