@@ -8,6 +8,8 @@ peak.  Also the small driver that `ncu` captures for the summaries under `profil
     python bench_kernels.py --only gemm_decode --case "lm_head M=8"   # one case
     python bench_kernels.py --only gemm_decode,moe_decode --rows 4,6   # the decode families at other token counts
     python bench_kernels.py --only attention_decode,attention_prefill --sink 0   # attention with a sink in the softmax
+    python bench_kernels.py --only attention_decode,attention_prefill --bias     # ... with a distance bias, learned sinks and gates per head
+    python bench_kernels.py --only attention_decode,attention_prefill --latent   # ... over latent rows (one plane, 16 heads on one kv head)
     python bench_kernels.py --only gated_less    # experts without a gate (squared ReLU), the junction of a loop,
                                                  # the embedding with learned positions
 
@@ -42,6 +44,9 @@ def main(argv=None):
     ap.add_argument("--experts", type=int, default=16, help="experts of the grouped products (128: Maverick's)")
     ap.add_argument("--rows", default="1,8,64", help="token counts of the decode families")
     ap.add_argument("--sink", type=float, default=None, help="attention cases run with a sink of this score in the softmax")
+    ap.add_argument("--bias", action="store_true", help="attention cases run with a distance bias, a learned sink and a gate per head")
+    ap.add_argument("--latent", action="store_true", help="attention cases run on a cache of one plane: 16 query heads on one kv head "
+                                                        "whose key rows (128 elements) are also the values, the result head by head")
     args = ap.parse_args(argv)
     dev = "cuda:0"
     torch.cuda.set_device(0)
@@ -209,6 +214,9 @@ def main(argv=None):
     # ---- attention over the paged cache
     P = 64
     sink = "" if args.sink is None else f" sink={args.sink}"
+    sink += (" bias+sinks+gates" if args.bias else "") + (" one plane, 16 heads on 1" if args.latent else "")
+    if args.latent:
+        nq, nkv, hd = 16, 1, 128
     def attention_case(fam, n_req, n_new, ctx, window):
         pages_per = -(-ctx // P)
         win = Window(*window)
@@ -219,15 +227,21 @@ def main(argv=None):
             off += n_new
         batch = build_step_batch(segs, [[0] * n_new] * n_req, [[]] * n_req, [tables], dev)
         def make():
-            kv = (torch.randn((2, n_req * pages_per, nkv, P, hd), device=dev) * 0.5).to(bf)
+            kv = (torch.randn((1 if args.latent else 2, n_req * pages_per, nkv, P, hd), device=dev) * 0.5).to(bf)
             q, out = rnd(off, nq * hd), torch.empty((off, nq * hd), dtype=bf, device=dev)
             cache = LayerCache(0, kv, None, P, False)
+            more = {}
+            if args.bias:
+                more = {"head_sinks": torch.randn(nq, device=dev), "head_gates": torch.rand((off, nq), device=dev),
+                        "head_slopes": torch.tensor([2.0 ** (-8.0 * (h + 1) / nq) for h in range(nq)], device=dev)}
+            if args.latent:
+                more["out_by_head"] = True
             return lambda: ks.paged_attention(q, out, batch, cache, num_heads=nq, window=win,
-                                              softmax_scale=1 / math.sqrt(hd), sink_logit=args.sink)
+                                              softmax_scale=1 / math.sqrt(hd), sink_logit=args.sink, **more)
         seen = sum(min(p + 1, ctx) - win.lowest_visible(p) for p in range(ctx - n_new, ctx)) / n_new
         if n_new == 1:
             # short launches: back to back over rotating copies of the cache, so no launch gap is counted
-            nbytes = int(n_req * seen * 2 * nkv * hd * 2)
+            nbytes = int(n_req * seen * (1 if args.latent else 2) * nkv * hd * 2)
             report(fam, f"requests={n_req} context={ctx} window={window[0]}{sink}", timed_rotating(make, nbytes), nbytes=nbytes)
             return
         report(fam, f"tokens={n_new} context={ctx} window={window[0]}{sink}", timed(make()),
@@ -258,6 +272,32 @@ def main(argv=None):
                                              qk_norm=QkNorm(1e-5), temperature=None)
             nbytes = M * ((nq + 2 * nkv) * hd * 2 + (nq + 2 * nkv) * hd * 2)
             report("small", f"qk_prepare M={M}", timed_rotating(make_prepare, max(nbytes, 64 << 20) if M == 8 else nbytes), nbytes=nbytes)
+
+    # ---- the kernels between the products of an attention through latents (q_rank 1024, rows of 96 + 32, 16 heads of 64 + 32)
+    if want("latent"):
+        from spite_b200.parts import Rotation
+        rq, rkv, dr, lh, dn, row = 1024, 96, 32, 16, 64, 128
+        rot = Rotation(torch.tensor([10000.0 ** (-2.0 * i / dr) for i in range(dr // 2)], dtype=torch.float32, device=dev), "neighbours", dr, 1.1)
+        for M in (8, 2048):
+            pages_per = -(-M // P) + 1
+            batch = build_step_batch([Segment(0, 0, 0, M, 0, True)], [[0] * M], [[]], [[list(range(pages_per))]], dev)
+            def make_prepare(M=M, batch=batch, pages_per=pages_per):
+                down = torch.randn((M, rq + rkv + dr + lh), device=dev)
+                cq, gates = torch.empty((M, rq), dtype=bf, device=dev), torch.empty((M, lh), dtype=torch.float32, device=dev)
+                cache = LayerCache(0, torch.zeros((1, pages_per, 1, P, row), dtype=bf, device=dev), None, P, True)
+                qg, kg = torch.ones(rq, device=dev), torch.ones(rkv, device=dev)
+                return lambda: ks.latent_prepare(down, cq, batch, cache, q_rank=rq, kv_rank=rkv, rotation=rot, q_gain=qg, kv_gain=kg,
+                                                 eps=1e-5, num_gates=lh, gates_out=gates)
+            nbytes = M * ((rq + rkv + dr + lh) * 4 + rq * 2 + row * 2 + lh * 4)
+            report("latent", f"latent_prepare M={M}", timed_rotating(make_prepare, max(nbytes, 64 << 20) if M == 8 else nbytes), nbytes=nbytes)
+            def make_queries(M=M, batch=batch):
+                q, qa = rnd(M, lh * (dn + dr)), torch.empty((M, lh * row), dtype=bf, device=dev)
+                qs = torch.empty((lh * M, dn), dtype=bf, device=dev)
+                rows, offs = torch.empty(lh * M, dtype=torch.int32, device=dev), torch.empty(lh + 1, dtype=torch.int32, device=dev)
+                return lambda: ks.latent_queries(q, qa, batch, num_heads=lh, head_dim=dn, kv_rank=rkv, rotation=rot, rows_out=rows,
+                                                 offsets_out=offs, sorted_out=qs)
+            nbytes = M * lh * ((dn + dr) * 2 + (row - rkv) * 2 + dn * 2 + 4)
+            report("latent", f"latent_queries M={M}", timed_rotating(make_queries, max(nbytes, 64 << 20) if M == 8 else nbytes), nbytes=nbytes)
 
     # ---- the small kernels of a decode step
     if want("small"):

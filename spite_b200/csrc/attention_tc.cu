@@ -320,9 +320,13 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                     const bool open = j0 >= lo_last && j0 + BN - 1 <= p_first;   // every key visible to every row with a token
                     // maximum of the raw scores (the scale is positive); four running values shorten the chain
                     float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+                    // The bias of key j0 + e is bias_raw * (j0 - pos) + bias_raw * e: the second term is one multiply-add an
+                    // element with a constant that the compiler knows; the first is the same for the whole tile and joins
+                    // the maximum and the exponent's offset below.
+                    const float tile_bias = biased ? bias_raw * (float)(j0 - pos) : 0.f;
                     if (biased) {
 #pragma unroll
-                        for (int e = 0; e < BN; ++e) s[e] = fmaf(bias_raw, (float)(j0 + e - pos), s[e]);
+                        for (int e = 0; e < BN; ++e) s[e] = fmaf(bias_raw, (float)e, s[e]);
                     }
                     if (!open) {                                   // a tile on a window's edge or on the diagonal
 #pragma unroll
@@ -333,11 +337,11 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                     }
 #pragma unroll
                     for (int e = 0; e < BN; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], s[e]);
-                    const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale;
+                    const float mx = (fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) + tile_bias) * scale;
                     const bool need = mx > m_ref + RESCALE_STEP;
                     float corr = 1.f;
                     if (need) { corr = exp2f(m_ref - mx); l *= corr; m_ref = mx; }
-                    const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref;
+                    const float neg_m = (m_ref == -INFINITY) ? 0.f : fmaf(tile_bias, scale, -m_ref);
                     // Over the key tiles that both own, the two row tiles take turns at the exponentials (key tile i
                     // of the first row tile, key tile i of the second, key tile i + 1 of the first, ...): the
                     // special-function units serve one at full rate while the tensor cores work for the other,
