@@ -77,7 +77,10 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const __grid_const
                                                               const int n_stages, const int ring_bytes,
                                                               const WaitControl waits) {
     constexpr int HD = 64 * NKB, NK = 4 * NKB;            // NK: 16-element steps of the head
-    constexpr int STAGE = 2 * NKB * BOX_BYTES;            // keys, then values
+    // a stage holds a tile of keys, then the tile of values; a cache of one plane (the key rows are the values) needs
+    // the one tile only, which the consumers then read both ways
+    const bool one_plane = c.v_offset == 0;
+    const int STAGE = (one_plane ? 1 : 2) * NKB * BOX_BYTES;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     Tail* tail = (Tail*)(smem + ring_bytes);               // the ring of stages, later the merge buffers, lie before it
@@ -135,7 +138,7 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const __grid_const
 #pragma unroll
         for (int kb = 0; kb < NKB; ++kb) {
             tma_load_2d_hint(dst + kb * BOX_BYTES, &map_k, kb * 64, row, bar, policy);
-            tma_load_2d_hint(dst + (NKB + kb) * BOX_BYTES, &map_v, kb * 64, row, bar, policy);
+            if (!one_plane) tma_load_2d_hint(dst + (NKB + kb) * BOX_BYTES, &map_v, kb * 64, row, bar, policy);
         }
     };
     int early = 0;                                            // tiles requested before the wait (producer thread only)
@@ -202,7 +205,7 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const __grid_const
         for (int ti = sb; ti < se; ++ti, s = (s + 1 == n_stages ? 0 : s + 1), ph ^= (s == 0)) {
             ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&tail->full[s]), ph, abort_flag, err_word, 2, wait_limit));
             if (!ok) break;
-            const unsigned kbase = smem_u32(smem + (size_t)s * STAGE), vbase = kbase + NKB * BOX_BYTES;
+            const unsigned kbase = smem_u32(smem + (size_t)s * STAGE), vbase = one_plane ? kbase : kbase + NKB * BOX_BYTES;
             const int j0 = ti * BN + 16 * warp;                  // this warp's first key
             // a warp whose 16 keys no row may see skips them (the first and the last tile of a window)
             if (j0 + 15 >= lo_first && j0 <= p_last) {
@@ -419,7 +422,7 @@ int launch(const AttentionParams& p, const StepTokens& b, const PagedCache& c, c
     cuuint32_t box[2] = {64, (cuuint32_t)BN};
     if (!make_map(&mk, c.kv, 2, dims, strides, box)) return SPITE_LAUNCH_FAILED;
     if (!make_map(&mv, (const __nv_bfloat16*)c.kv + c.v_offset, 2, dims, strides, box)) return SPITE_LAUNCH_FAILED;
-    const size_t stage = 2 * (size_t)NKB * BOX_BYTES;
+    const size_t stage = (c.v_offset == 0 ? 1 : 2) * (size_t)NKB * BOX_BYTES;   // (one plane: the key tile is the value tile)
     const size_t merge = (size_t)CONSUMERS * 16 * hd * 4 + CONSUMERS * 16 * 2 * 4;
     const size_t weights = (size_t)(2 * 16 * x.n_splits + 16) * 4;
     size_t ring = (size_t)n_stages * stage;
